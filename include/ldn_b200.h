@@ -1,0 +1,156 @@
+/*
+ * C ABI of libldn_b200.so -- sm_100a kernels for the L_p-distance operator
+ *     y[b, o, hw] = ( sum_c |x[b, g, c, hw] - w[g, o, c]|^p )^(1/p)
+ * of zbh2047/L_inf-dist-net-v2, its backward pass and its p = inf interval-bound variant.
+ *
+ * Each entry point replaces one static launcher of the reference's core/cuda/norm_dist.h (cited per
+ * function) as it is reached through the pybind wrappers of core/cuda/norm_dist.cpp:40-189.  Argument
+ * order follows those launchers; two things are added: the CUDA stream to launch on (the reference
+ * uses the legacy default stream) and an int return value (0 = success, see ldn_status_string).
+ *
+ * Conventions (identical to the reference):
+ *   - all pointers are device pointers to contiguous fp32 (int32 for pos arrays) on the current device;
+ *   - x[B, CI, HW], w[CO, CI/G], y[B, CO, HW]; element offsets
+ *       x: ((b*G + g)*(CI/G) + c)*HW + hw,  w: (g*(CO/G) + o)*(CI/G) + c,  y: ((b*G + g)*(CO/G) + o)*HW + hw;
+ *   - the caller allocates every output; outputs need not be zeroed, the library zero-fills wherever
+ *     it accumulates;
+ *   - pos arrays have the layout of y; bit 31 is a flag, bits 0..30 the channel index in the group.
+ * Sizes are 32-bit per dimension but all offsets are computed in 64 bits.
+ *
+ * Scratch: kernels that need intermediate device memory take it from a per-(device, stream) arena that
+ * the library allocates on first use and grows on demand (cudaMalloc; a growth synchronises the stream).
+ * Calls issued on the same stream may follow each other freely; the same stream must not be used from
+ * two host threads at once.
+ */
+#ifndef LDN_B200_H
+#define LDN_B200_H
+
+#if defined(__GNUC__)
+#define LDN_API __attribute__((visibility("default")))
+#else
+#define LDN_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ldn_stream_t; /* == cudaStream_t */
+
+/* Human-readable text for a status code returned by any function below. */
+LDN_API const char* ldn_status_string(int status);
+
+/* Library / build identification: "ldn_b200 <version> sm_100a". */
+LDN_API const char* ldn_version(void);
+
+/*
+ * Copies the device status word of the stream's arena to the host, waits for the stream, clears the
+ * word and returns it (0 when every kernel so far completed normally; 4 when a bounded wait inside a
+ * kernel gave up).  No counterpart in the reference, which never checks launch results.
+ */
+LDN_API int ldn_check_status(ldn_stream_t stream);
+
+/* Releases every scratch arena of the current device (synchronises the device). */
+LDN_API int ldn_release_scratch(void);
+
+/*
+ * Test hook: cap the number of persistent CTAs of the tile kernels (0 = one per SM).  Lets tests force
+ * output tiles to be shared between CTAs on small problems.
+ */
+LDN_API void ldn_set_max_ctas(int max_ctas);
+
+/* ---- finite p ------------------------------------------------------------------------------- */
+
+/*
+ * Replaces norm_dist<ip>::forward_with_max(max = nullptr) for p <= 10 and norm_dist<ip>::forward for
+ * p > 10 (core/cuda/norm_dist.h:5-8, selected in core/cuda/norm_dist.cpp:40-53).
+ *   p <= 10: y = max(sum |t|^p, 1.175494351e-38)^(1/p);  p > 10: y = M (sum (|t|/M)^p + (1e-10/M)^p)^(1/p),
+ *   M = max(1e-10, max |t|).  Requires p > 0 and finite.
+ */
+LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                          float* output, float p, ldn_stream_t stream);
+
+/*
+ * Replaces norm_dist<ip>::forward_with_max with a caller-supplied normaliser (core/cuda/norm_dist.h:7-8,
+ * core/cuda/norm_dist.cpp:55-64): r = 1/max_output; y = (sum (|t| r)^p + (1e-10 r)^p)^(1/p) / r.
+ */
+LDN_API int ldn_norm_dist_forward_with_max(const float* input, const float* weight, const float* max_output,
+                                   int B, int CO, int CI, int G, int HW, float* output, float p,
+                                   ldn_stream_t stream);
+
+/*
+ * Replaces norm_dist<ip>::backward_input (core/cuda/norm_dist.h:9-10, core/cuda/norm_dist.cpp:66-77):
+ *   grad_input[b, c] = sum_o grad_output * sgn(t) * (|t| / output)^(p-1),  sgn(t) = +1 for t >= 0.
+ */
+LDN_API int ldn_norm_dist_backward_input(const float* grad_output, const float* input, const float* weight,
+                                 const float* output, int B, int CO, int CI, int G, int HW,
+                                 float* grad_input, float p, ldn_stream_t stream);
+
+/*
+ * Replaces norm_dist<ip>::backward_input_weight (core/cuda/norm_dist.h:11-13, core/cuda/norm_dist.cpp:79-91):
+ * grad_input as above and grad_weight[o, c] = -sum_{b,hw} of the same term.  grad_input may be NULL when
+ * the caller does not need it (the reference always computes it).  Results are deterministic: no atomics.
+ */
+LDN_API int ldn_norm_dist_backward_input_weight(const float* grad_output, const float* input, const float* weight,
+                                        const float* output, int B, int CO, int CI, int G, int HW,
+                                        float* grad_input, float* grad_weight, float p, ldn_stream_t stream);
+
+/* ---- p = inf -------------------------------------------------------------------------------- */
+
+/* Replaces inf_dist::forward_nograd (core/cuda/norm_dist.h:17-18): y = max(1e-10, max |t|). */
+LDN_API int ldn_inf_dist_forward_nograd(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                                float* output, ldn_stream_t stream);
+
+/*
+ * Replaces inf_dist::forward (core/cuda/norm_dist.h:19-20): the value above and
+ * pos = first channel attaining it | (t < 0 ? 1 << 31 : 0); pos = 0 when no |t| exceeds 1e-10.
+ */
+LDN_API int ldn_inf_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                         float* output, int* pos, ldn_stream_t stream);
+
+/* Replaces inf_dist::backward_input (core/cuda/norm_dist.h:21-22): grad_input[b, idx] += (pos >= 0 ? g : -g). */
+LDN_API int ldn_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
+                                float* grad_input, ldn_stream_t stream);
+
+/*
+ * Replaces inf_dist::backward_input_weight (core/cuda/norm_dist.h:23-24): as above plus
+ * grad_weight[o, idx] -= (pos >= 0 ? g : -g).  grad_input may be NULL.
+ */
+LDN_API int ldn_inf_dist_backward_input_weight(const float* grad_output, const int* pos, int B, int CO, int CI, int G,
+                                       int HW, float* grad_input, float* grad_weight, ldn_stream_t stream);
+
+/* ---- p = inf interval bounds ----------------------------------------------------------------- */
+
+/*
+ * Replaces bound_inf_dist::forward_nograd (core/cuda/norm_dist.h:28-29).  With t1 = w - xL, t2 = xU - w
+ * (elements with xL > xU are first replaced by their midpoint):
+ *   yL = max(1e-10, max_c -min(t1, t2)),  yU = max(1e-10, max_c max(t1, t2)).
+ */
+LDN_API int ldn_bound_inf_dist_forward_nograd(const float* inputL, const float* inputU, const float* weight,
+                                      int B, int CO, int CI, int G, int HW, float* outputL, float* outputU,
+                                      ldn_stream_t stream);
+
+/*
+ * Replaces bound_inf_dist::forward (core/cuda/norm_dist.h:30-31): the bounds above plus posL / posU =
+ * first channel attaining the bound | (t1 <= t2 ? 0 : 1 << 31); posL = 0xffffffff when the lower bound is
+ * the 1e-10 floor (no gradient), posU = 0 when the upper bound is the floor.
+ */
+LDN_API int ldn_bound_inf_dist_forward(const float* inputL, const float* inputU, const float* weight,
+                               int B, int CO, int CI, int G, int HW, float* outputL, float* outputU,
+                               int* posL, int* posU, ldn_stream_t stream);
+
+/* Replaces bound_inf_dist::backward_input (core/cuda/norm_dist.h:32-34). */
+LDN_API int ldn_bound_inf_dist_backward_input(const float* grad_outputL, const float* grad_outputU,
+                                      const int* posL, const int* posU, int B, int CO, int CI, int G, int HW,
+                                      float* grad_inputL, float* grad_inputU, ldn_stream_t stream);
+
+/* Replaces bound_inf_dist::backward_input_weight (core/cuda/norm_dist.h:35-37). */
+LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, const float* grad_outputU,
+                                             const int* posL, const int* posU, int B, int CO, int CI, int G,
+                                             int HW, float* grad_inputL, float* grad_inputU, float* grad_weight,
+                                             ldn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LDN_B200_H */

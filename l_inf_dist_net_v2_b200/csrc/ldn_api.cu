@@ -1,0 +1,486 @@
+// C-ABI entry points (include/ldn_b200.h): argument checks, choice of operand views (the caller's
+// arrays where TMA can read them directly, canonical copies in scratch otherwise), tile-engine plans.
+#include <math.h>
+#include <string.h>
+
+#include "ldn_b200.h"
+#include "ldn_launch.cuh"
+#include "ldn_prep.cuh"
+
+namespace ldn {
+int release_arenas();
+
+namespace {
+
+int g_max_ctas = 0;
+
+// A 3-D view of an operand for TMA: `inner` contiguous elements, `rows` rows, `groups` groups.
+// row_coord tells which tensor-map coordinate carries the row (1: dims are (inner, rows, groups);
+// 2: dims are (inner, groups, rows), used when the group stride is the smaller one).
+struct View {
+    const float* ptr;
+    long long inner, rows, groups;
+    long long stride_row, stride_group;
+    int row_coord;
+};
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int ceil4(int v) { return (v + 3) & ~3; }
+
+inline View canonical_view(const float* ptr, long long inner, long long rows, long long groups) {
+    const long long pitch = ceil4(static_cast<int>(inner));
+    return View{ptr, inner, rows, groups, pitch, rows * pitch, 1};
+}
+inline size_t canonical_floats(long long inner, long long rows, long long groups) {
+    return static_cast<size_t>(ceil4(static_cast<int>(inner))) * rows * groups;
+}
+
+int build_map(CUtensorMap* map, const View& v, Layout layout) {
+    const unsigned bi = layout == Layout::RowMajor ? kTileK : kTileN;
+    const unsigned br = layout == Layout::RowMajor ? kTileM : kTileK;
+    unsigned long long dims[3], strides[2];
+    unsigned box[3];
+    dims[0] = v.inner;
+    box[0] = bi;
+    if (v.row_coord == 1) {
+        dims[1] = v.rows; dims[2] = v.groups;
+        strides[0] = v.stride_row; strides[1] = v.stride_group;
+        box[1] = br; box[2] = 1;
+    } else {
+        dims[1] = v.groups; dims[2] = v.rows;
+        strides[0] = v.stride_group; strides[1] = v.stride_row;
+        box[1] = 1; box[2] = br;
+    }
+    return make_tensor_map(map, v.ptr, dims, strides, box, layout == Layout::RowMajor);
+}
+
+inline Operand as_operand(const View& v) { return Operand{v.ptr, v.stride_row, v.stride_group}; }
+
+int check_shape(int B, int CO, int CI, int G, int HW, Shape* s) {
+    if (B <= 0 || CO <= 0 || CI <= 0 || G <= 0 || HW <= 0) return kBadArgument;
+    if (CI % G != 0 || CO % G != 0) return kBadArgument;
+    s->B = B; s->CO = CO; s->CI = CI; s->G = G; s->HW = HW;
+    s->CIg = CI / G; s->COg = CO / G;
+    s->M = static_cast<long long>(B) * HW;
+    if (s->M > 0x7fffffffLL) return kBadArgument;
+    return kOk;
+}
+
+struct Call {
+    const DeviceCtx* ctx;
+    Arena* arena;
+    Bump bump;
+    cudaStream_t st;
+    int cap;  // persistent CTAs
+};
+
+int begin_call(Call* c, ldn_stream_t stream, size_t scratch_bytes) {
+    int r = get_device_ctx(&c->ctx);
+    if (r != kOk) return r;
+    c->st = reinterpret_cast<cudaStream_t>(stream);
+    c->cap = (g_max_ctas > 0 && g_max_ctas < c->ctx->sm_count) ? g_max_ctas : c->ctx->sm_count;
+    r = get_arena(c->st, scratch_bytes, &c->arena);
+    if (r != kOk) return r;
+    c->bump = Bump{c->arena->base, 0, c->arena->capacity};
+    return kOk;
+}
+
+inline size_t partial_bytes(int cap, int arrays) {
+    return pad256(static_cast<size_t>(cap) * 2 * arrays * kTileElems * sizeof(float));
+}
+inline int cap_for(const DeviceCtx* ctx) {
+    return (g_max_ctas > 0 && g_max_ctas < ctx->sm_count) ? g_max_ctas : ctx->sm_count;
+}
+
+// The x operand as the engine reads it: the caller's array when it is fully connected (HW == 1) with a
+// 16-byte aligned base and row length, else a canonical copy [g][m][pitch] made by `copy`.
+bool x_is_natural(const float* x, const Shape& s) { return s.HW == 1 && s.CIg % 4 == 0 && aligned16(x); }
+View x_natural_view(const float* x, const Shape& s) {
+    if (s.G == 1) return View{x, s.CIg, s.M, 1, s.CI, s.M * s.CI, 1};
+    return View{x, s.CIg, s.M, s.G, s.CI, s.CIg, 2};
+}
+bool w_is_natural(const float* w, const Shape& s) { return s.CIg % 4 == 0 && aligned16(w); }
+View w_natural_view(const float* w, const Shape& s) {
+    return View{w, s.CIg, s.COg, s.G, s.CIg, static_cast<long long>(s.COg) * s.CIg, 1};
+}
+
+size_t x_scratch_bytes(const float* x, const Shape& s) {
+    return x_is_natural(x, s) ? 0 : pad256(canonical_floats(s.CIg, s.M, s.G) * sizeof(float));
+}
+size_t w_scratch_bytes(const float* w, const Shape& s) {
+    return w_is_natural(w, s) ? 0 : pad256(canonical_floats(s.CIg, s.COg, s.G) * sizeof(float));
+}
+
+int get_x_view(Call& c, const float* x, const Shape& s, View* v) {
+    if (x_is_natural(x, s)) {
+        *v = x_natural_view(x, s);
+        return kOk;
+    }
+    float* xc = c.bump.take<float>(canonical_floats(s.CIg, s.M, s.G));
+    if (!xc) return kWorkspace;
+    *v = canonical_view(xc, s.CIg, s.M, s.G);
+    return launch_canon_x(x, xc, s, static_cast<int>(v->stride_row), c.st);
+}
+int get_w_view(Call& c, const float* w, const Shape& s, View* v) {
+    if (w_is_natural(w, s)) {
+        *v = w_natural_view(w, s);
+        return kOk;
+    }
+    float* wc = c.bump.take<float>(canonical_floats(s.CIg, s.COg, s.G));
+    if (!wc) return kWorkspace;
+    *v = canonical_view(wc, s.CIg, s.COg, s.G);
+    return launch_canon_w(w, wc, s, static_cast<int>(v->stride_row), c.st);
+}
+
+// Common part of a tile-engine plan.
+int fill_plan(Call& c, TileLaunch* L, long long M, int N, int K, int G, int arrays) {
+    memset(L, 0, sizeof(*L));
+    TileParams& P = L->params;
+    P.M = static_cast<int>(M); P.N = N; P.K = K; P.G = G;
+    P.tiles_m = static_cast<int>((M + kTileM - 1) / kTileM);
+    P.tiles_n = (N + kTileN - 1) / kTileN;
+    P.kt = (K + kTileK - 1) / kTileK;
+    P.total_iters = static_cast<long long>(G) * P.tiles_m * P.tiles_n * P.kt;
+    L->grid = static_cast<int>(P.total_iters < c.cap ? P.total_iters : c.cap);
+    P.partials = c.bump.take<float>(static_cast<size_t>(L->grid) * 2 * arrays * kTileElems);
+    if (!P.partials) return kWorkspace;
+    P.status = c.arena->status;
+    return kOk;
+}
+
+OutAddr y_addr(const Shape& s) {
+    return OutAddr{static_cast<long long>(s.CO) * s.HW, 1, static_cast<long long>(s.COg) * s.HW, s.HW, s.HW};
+}
+OutAddr x_addr(const Shape& s) {
+    return OutAddr{static_cast<long long>(s.CI) * s.HW, 1, static_cast<long long>(s.CIg) * s.HW, s.HW, s.HW};
+}
+OutAddr w_addr(const Shape& s) {
+    return OutAddr{s.CIg, 0, static_cast<long long>(s.COg) * s.CIg, 1, 1};
+}
+
+// forward-type problem: out (m = (b, hw), n = o), k = c
+int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, const View& wv, const Shape& s,
+                float* out0, float* out1, int* outi0, int* outi1, const float* pres, float p) {
+    TileLaunch L;
+    int r = fill_plan(c, &L, s.M, s.COg, s.CIg, s.G, fwd_acc_arrays(kind));
+    if (r != kOk) return r;
+    TileParams& P = L.params;
+    P.a_row_coord = a0.row_coord;
+    P.b_row_coord = wv.row_coord;
+    P.a0 = as_operand(a0);
+    P.a1 = a1 ? as_operand(*a1) : P.a0;
+    P.b = as_operand(wv);
+    P.pres = Operand{pres, 0, 0};
+    P.out = y_addr(s);
+    P.out_f0 = out0; P.out_f1 = out1; P.out_i0 = outi0; P.out_i1 = outi1;
+    P.p = p; P.q = p - 1.0f;
+    if ((r = build_map(&L.map_a0, a0, Layout::RowMajor)) != kOk) return r;
+    if ((r = build_map(&L.map_a1, a1 ? *a1 : a0, Layout::RowMajor)) != kOk) return r;
+    if ((r = build_map(&L.map_b, wv, Layout::RowMajor)) != kOk) return r;
+    switch (kind) {
+        case FwdKind::PowInt:
+        case FwdKind::PowGen:
+        case FwdKind::PowNorm: return launch_fwd_pow(kind, ip, L, c.st);
+        default: return launch_fwd_inf(kind, L, c.st);
+    }
+}
+
+// integer template value the reference dispatch would use for exponent e (norm_dist.cpp:17-35)
+int int_power(float e) {
+    if (e == static_cast<float>(static_cast<int>(e)) && static_cast<int>(e) >= 0 && static_cast<int>(e) <= 8)
+        return static_cast<int>(e);
+    return -1;
+}
+
+int norm_dist_backward(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
+                       float* gw, float p, ldn_stream_t stream) {
+    if (!go || !x || !w || !y || (!gx && !gw)) return kBadArgument;
+    if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
+    const DeviceCtx* ctx;
+    int r = get_device_ctx(&ctx);
+    if (r != kOk) return r;
+    const int cap = cap_for(ctx);
+    const int iq = int_power(p - 1.0f);
+    const int ncoef = iq >= 0 ? 1 : 2;
+    const size_t coef_floats = canonical_floats(s.COg, s.M, s.G);
+    size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + ncoef * pad256(coef_floats * sizeof(float)) +
+                  2 * partial_bytes(cap, 1);
+    Call c;
+    if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    View xv, wv;
+    if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
+    if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
+    float* c0 = c.bump.take<float>(coef_floats);
+    float* c1 = ncoef == 2 ? c.bump.take<float>(coef_floats) : nullptr;
+    if (!c0 || (ncoef == 2 && !c1)) return kWorkspace;
+    const View cv0 = canonical_view(c0, s.COg, s.M, s.G);
+    const View cv1 = canonical_view(c1 ? c1 : c0, s.COg, s.M, s.G);
+    if (iq >= 0) r = launch_coef_int(go, y, c0, s, static_cast<int>(cv0.stride_row), iq, c.st);
+    else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(cv0.stride_row), c.st);
+    if (r != kOk) return r;
+
+    if (gx) {
+        // out (m = (b, hw), n = c), k = o
+        TileLaunch L;
+        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1)) != kOk) return r;
+        TileParams& P = L.params;
+        P.a_row_coord = cv0.row_coord;
+        P.b_row_coord = wv.row_coord;
+        P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(wv);
+        P.pres = as_operand(xv);
+        P.out = x_addr(s);
+        P.out_f0 = gx;
+        P.p = p; P.q = p - 1.0f;
+        if ((r = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_b, wv, Layout::KMajor)) != kOk) return r;
+        if ((r = launch_bwd_x(iq, L, c.st)) != kOk) return r;
+    }
+    if (gw) {
+        // out (m = o, n = c), k = (b, hw)
+        TileLaunch L;
+        if ((r = fill_plan(c, &L, s.COg, s.CIg, static_cast<int>(s.M), s.G, 1)) != kOk) return r;
+        TileParams& P = L.params;
+        P.a_row_coord = cv0.row_coord;
+        P.b_row_coord = xv.row_coord;
+        P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(xv);
+        P.pres = as_operand(wv);
+        P.out = w_addr(s);
+        P.out_f0 = gw;
+        P.p = p; P.q = p - 1.0f;
+        if ((r = build_map(&L.map_a0, cv0, Layout::KMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_a1, cv1, Layout::KMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_b, xv, Layout::KMajor)) != kOk) return r;
+        if ((r = launch_bwd_w(iq, L, c.st)) != kOk) return r;
+    }
+    return kOk;
+}
+
+int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* pos, ldn_stream_t stream) {
+    if (!x || !w || !y) return kBadArgument;
+    const DeviceCtx* ctx;
+    int r = get_device_ctx(&ctx);
+    if (r != kOk) return r;
+    const FwdKind kind = pos ? FwdKind::InfPos : FwdKind::Inf;
+    size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + partial_bytes(cap_for(ctx), fwd_acc_arrays(kind));
+    Call c;
+    if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    View xv, wv;
+    if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
+    if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
+    return run_forward(c, kind, 0, xv, nullptr, wv, s, y, nullptr, pos, nullptr, nullptr, INFINITY);
+}
+
+int bound_forward(const float* xl, const float* xu, const float* w, const Shape& s, float* yl, float* yu, int* pl,
+                  int* pu, ldn_stream_t stream) {
+    if (!xl || !xu || !w || !yl || !yu || ((pl == nullptr) != (pu == nullptr))) return kBadArgument;
+    const DeviceCtx* ctx;
+    int r = get_device_ctx(&ctx);
+    if (r != kOk) return r;
+    const size_t xfloats = canonical_floats(s.CIg, s.M, s.G);
+    size_t need = 2 * pad256(xfloats * sizeof(float)) + w_scratch_bytes(w, s) + 2 * partial_bytes(cap_for(ctx), 2);
+    Call c;
+    if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    float* lc = c.bump.take<float>(xfloats);
+    float* uc = c.bump.take<float>(xfloats);
+    if (!lc || !uc) return kWorkspace;
+    const View lv = canonical_view(lc, s.CIg, s.M, s.G);
+    const View uv = canonical_view(uc, s.CIg, s.M, s.G);
+    if ((r = launch_canon_bounds(xl, xu, lc, uc, s, static_cast<int>(lv.stride_row), c.st)) != kOk) return r;
+    View wv;
+    if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
+    if (!pl) return run_forward(c, FwdKind::Bound, 0, lv, &uv, wv, s, yl, yu, nullptr, nullptr, nullptr, INFINITY);
+    r = run_forward(c, FwdKind::BoundPosLower, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
+    if (r != kOk) return r;
+    return run_forward(c, FwdKind::BoundPosUpper, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
+}
+
+}  // namespace
+}  // namespace ldn
+
+using namespace ldn;
+
+extern "C" {
+
+LDN_API const char* ldn_status_string(int status) {
+    switch (status) {
+        case kOk: return "ok";
+        case kBadArgument: return "bad argument (null pointer, non-positive size, CI or CO not divisible by G, or p not a positive finite number)";
+        case kNoDevice: return "no usable CUDA device or driver entry point";
+        case kWorkspace: return "scratch memory could not be provided";
+        case kDeviceTimeout: return "a bounded wait inside a kernel gave up";
+        case kTensorMap: return "the driver rejected a TMA descriptor";
+        default: break;
+    }
+    if (status >= kCudaBase) return cudaGetErrorString(static_cast<cudaError_t>(status - kCudaBase));
+    return "unknown status";
+}
+
+LDN_API const char* ldn_version(void) { return "ldn_b200 0.1 sm_100a"; }
+
+LDN_API void ldn_set_max_ctas(int max_ctas) { g_max_ctas = max_ctas > 0 ? max_ctas : 0; }
+
+LDN_API int ldn_release_scratch(void) { return release_arenas(); }
+
+LDN_API int ldn_check_status(ldn_stream_t stream) {
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    Arena* arena;
+    int r = get_arena(st, 0, &arena);
+    if (r != kOk) return r;
+    cudaError_t e = cudaMemcpyAsync(arena->status_host, arena->status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(arena->status, 0, sizeof(int), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_status(e);
+    const int v = *arena->status_host;
+    *arena->status_host = 0;
+    return v;
+}
+
+LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                          float* output, float p, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!input || !weight || !output) return kBadArgument;
+    if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
+    const DeviceCtx* ctx;
+    if ((r = get_device_ctx(&ctx)) != kOk) return r;
+    const bool normalised = p > 10.0f;  // MIN_NORMALIZED_P of the reference
+    const size_t ybytes = pad256(sizeof(float) * static_cast<size_t>(B) * CO * HW);
+    size_t need = x_scratch_bytes(input, s) + w_scratch_bytes(weight, s) + 2 * partial_bytes(cap_for(ctx), 1) +
+                  (normalised ? ybytes : 0);
+    Call c;
+    if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    View xv, wv;
+    if ((r = get_x_view(c, input, s, &xv)) != kOk) return r;
+    if ((r = get_w_view(c, weight, s, &wv)) != kOk) return r;
+    if (!normalised) {
+        const int ip = int_power(p);
+        if (ip >= 1) return run_forward(c, FwdKind::PowInt, ip, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, p);
+        return run_forward(c, FwdKind::PowGen, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, p);
+    }
+    float* mbuf = c.bump.take<float>(static_cast<size_t>(B) * CO * HW);
+    if (!mbuf) return kWorkspace;
+    r = run_forward(c, FwdKind::Inf, 0, xv, nullptr, wv, s, mbuf, nullptr, nullptr, nullptr, nullptr, INFINITY);
+    if (r != kOk) return r;
+    return run_forward(c, FwdKind::PowNorm, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, mbuf, p);
+}
+
+LDN_API int ldn_norm_dist_forward_with_max(const float* input, const float* weight, const float* max_output,
+                                   int B, int CO, int CI, int G, int HW, float* output, float p,
+                                   ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!input || !weight || !max_output || !output) return kBadArgument;
+    if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
+    const DeviceCtx* ctx;
+    if ((r = get_device_ctx(&ctx)) != kOk) return r;
+    size_t need = x_scratch_bytes(input, s) + w_scratch_bytes(weight, s) + partial_bytes(cap_for(ctx), 1);
+    Call c;
+    if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    View xv, wv;
+    if ((r = get_x_view(c, input, s, &xv)) != kOk) return r;
+    if ((r = get_w_view(c, weight, s, &wv)) != kOk) return r;
+    return run_forward(c, FwdKind::PowNorm, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, max_output, p);
+}
+
+LDN_API int ldn_norm_dist_backward_input(const float* grad_output, const float* input, const float* weight,
+                                 const float* output, int B, int CO, int CI, int G, int HW,
+                                 float* grad_input, float p, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!grad_input) return kBadArgument;
+    return norm_dist_backward(grad_output, input, weight, output, s, grad_input, nullptr, p, stream);
+}
+
+LDN_API int ldn_norm_dist_backward_input_weight(const float* grad_output, const float* input, const float* weight,
+                                        const float* output, int B, int CO, int CI, int G, int HW,
+                                        float* grad_input, float* grad_weight, float p, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!grad_weight) return kBadArgument;
+    return norm_dist_backward(grad_output, input, weight, output, s, grad_input, grad_weight, p, stream);
+}
+
+LDN_API int ldn_inf_dist_forward_nograd(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                                float* output, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    return inf_forward(input, weight, s, output, nullptr, stream);
+}
+
+LDN_API int ldn_inf_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                         float* output, int* pos, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!pos) return kBadArgument;
+    return inf_forward(input, weight, s, output, pos, stream);
+}
+
+LDN_API int ldn_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
+                                float* grad_input, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!grad_output || !pos || !grad_input) return kBadArgument;
+    return launch_inf_scatter(grad_output, pos, grad_input, nullptr, s, reinterpret_cast<cudaStream_t>(stream));
+}
+
+LDN_API int ldn_inf_dist_backward_input_weight(const float* grad_output, const int* pos, int B, int CO, int CI, int G,
+                                       int HW, float* grad_input, float* grad_weight, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!grad_output || !pos || !grad_weight) return kBadArgument;
+    return launch_inf_scatter(grad_output, pos, grad_input, grad_weight, s, reinterpret_cast<cudaStream_t>(stream));
+}
+
+LDN_API int ldn_bound_inf_dist_forward_nograd(const float* inputL, const float* inputU, const float* weight,
+                                      int B, int CO, int CI, int G, int HW, float* outputL, float* outputU,
+                                      ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    return bound_forward(inputL, inputU, weight, s, outputL, outputU, nullptr, nullptr, stream);
+}
+
+LDN_API int ldn_bound_inf_dist_forward(const float* inputL, const float* inputU, const float* weight,
+                               int B, int CO, int CI, int G, int HW, float* outputL, float* outputU,
+                               int* posL, int* posU, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!posL || !posU) return kBadArgument;
+    return bound_forward(inputL, inputU, weight, s, outputL, outputU, posL, posU, stream);
+}
+
+LDN_API int ldn_bound_inf_dist_backward_input(const float* grad_outputL, const float* grad_outputU,
+                                      const int* posL, const int* posU, int B, int CO, int CI, int G, int HW,
+                                      float* grad_inputL, float* grad_inputU, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!grad_outputL || !grad_outputU || !posL || !posU || !grad_inputL || !grad_inputU) return kBadArgument;
+    return launch_bound_scatter(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, nullptr, s,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, const float* grad_outputU,
+                                             const int* posL, const int* posU, int B, int CO, int CI, int G,
+                                             int HW, float* grad_inputL, float* grad_inputU, float* grad_weight,
+                                             ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!grad_outputL || !grad_outputU || !posL || !posU || !grad_inputL || !grad_inputU || !grad_weight)
+        return kBadArgument;
+    return launch_bound_scatter(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, grad_weight, s,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,27 @@
+// Non-template launch entry points of the tile-engine instantiations (one translation unit per family
+// so that they compile in parallel).
+#pragma once
+#include "ldn_tile.cuh"
+
+namespace ldn {
+
+enum class FwdKind { PowInt, PowGen, PowNorm, Inf, InfPos, Bound, BoundPosLower, BoundPosUpper };
+
+// number of accumulator arrays (float + int) an op keeps per output: sizes the stream-K scratch
+inline int fwd_acc_arrays(FwdKind k) {
+    switch (k) {
+        case FwdKind::InfPos: return 2;
+        case FwdKind::Bound: return 2;
+        case FwdKind::BoundPosLower: return 2;
+        case FwdKind::BoundPosUpper: return 2;
+        default: return 1;
+    }
+}
+inline int fwd_num_a(FwdKind k) { return (k == FwdKind::Bound || k == FwdKind::BoundPosLower || k == FwdKind::BoundPosUpper) ? 2 : 1; }
+
+int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st);   // PowInt (ip 1..8), PowGen, PowNorm
+int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper}
+int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st);                   // iq 0..8, or -1 for general p
+int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st);
+
+}  // namespace ldn

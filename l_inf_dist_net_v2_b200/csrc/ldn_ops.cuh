@@ -1,0 +1,360 @@
+// Per-pair arithmetic of every kernel family, as policy classes for the tile engine (ldn_tile.cuh).
+//
+// Every op is written so that zero-filled operand elements (TMA out-of-range fill) are neutral:
+// |0 - 0|^p = 0 for p > 0, |0 - 0| never exceeds the 1e-10 floor, and backward coefficients of padded
+// entries are zero.
+#pragma once
+#include <float.h>
+#include "ldn_tile.cuh"
+
+namespace ldn {
+
+constexpr float kEps = 1e-10f;                  // value floor of the p = inf family and of the p > 10 sum
+constexpr float kUnderflow = 1.175494351e-38f;  // floor of the p <= 10 sum before the root
+constexpr int kSignBit = static_cast<int>(0x80000000u);
+constexpr int kNoGrad = static_cast<int>(0xffffffffu);
+
+__device__ __forceinline__ float lg2_approx(float x) {
+    float r;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// |t|^IP by repeated multiplication, IP in 1..8
+template <int IP>
+__device__ __forceinline__ float abs_pow(float t) {
+    static_assert(IP >= 1 && IP <= 8, "integer power out of range");
+    const float a = fabsf(t);
+    if (IP == 1) return a;
+    const float t2 = t * t;
+    if (IP == 2) return t2;
+    if (IP == 3) return t2 * a;
+    const float t4 = t2 * t2;
+    if (IP == 4) return t4;
+    if (IP == 5) return t4 * a;
+    if (IP == 6) return t4 * t2;
+    if (IP == 7) return t4 * (t2 * a);
+    return t4 * t4;
+}
+
+// acc + |t|^IP with the last multiply fused into the accumulation
+template <int IP>
+__device__ __forceinline__ float acc_abs_pow(float acc, float t) {
+    const float a = fabsf(t);
+    if (IP == 1) return acc + a;
+    if (IP == 2) return fmaf(t, t, acc);
+    const float t2 = t * t;
+    if (IP == 3) return fmaf(t2, a, acc);
+    if (IP == 4) return fmaf(t2, t2, acc);
+    const float t4 = t2 * t2;
+    if (IP == 5) return fmaf(t4, a, acc);
+    if (IP == 6) return fmaf(t4, t2, acc);
+    if (IP == 7) return fmaf(t4, t2 * a, acc);
+    return fmaf(t4, t4, acc);
+}
+
+// sgn(t) |t|^IQ with sgn(t) = +1 for t >= 0 (IQ in 0..8); used by the backward kernels
+template <int IQ>
+__device__ __forceinline__ float signed_pow(float t) {
+    static_assert(IQ >= 0 && IQ <= 8, "integer power out of range");
+    if (IQ == 0) return t >= 0.0f ? 1.0f : -1.0f;
+    if (IQ == 1) return t;
+    const float u = t * fabsf(t);  // sgn(t) t^2
+    if (IQ == 2) return u;
+    const float t2 = t * t;
+    if (IQ == 3) return t2 * t;
+    if (IQ == 4) return t2 * u;
+    const float t4 = t2 * t2;
+    if (IQ == 5) return t4 * t;
+    if (IQ == 6) return t4 * u;
+    if (IQ == 7) return t4 * (t2 * t);
+    return (t4 * t2) * u;
+}
+
+__device__ __forceinline__ float max4abs(float a, float b, float c, float d) {
+    return fmaxf(fmaxf(fmaxf(fabsf(a), fabsf(b)), fabsf(c)), fabsf(d));
+}
+
+struct FwdLayout {
+    static constexpr Layout LA = Layout::RowMajor;
+    static constexpr Layout LB = Layout::RowMajor;
+};
+
+// ------------------------------------------------------------------------------------------------
+// Finite p, forward
+// ------------------------------------------------------------------------------------------------
+
+// sum of |t|^IP, then the p-th root with the underflow floor
+template <int IP>
+struct FwdPowInt : FwdLayout {
+    static constexpr int NUM_A = 1, NF = 1, NI = 0;
+    static constexpr bool HAS_P = false;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static void update4(float* f, int*, float, const float* a, const float*, const float* b, int,
+                                   const TileParams&) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f[0] = acc_abs_pow<IP>(f[0], a[k] - b[k]);
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        P.out_f0[out_offset(P.out, m, n, g)] = powf(fmaxf(f[0], kUnderflow), 1.0f / P.p);
+    }
+};
+
+// sum of |t|^p = 2^(p lg2 |t|) for non-integer (or > 8) p <= 10
+struct FwdPowGen : FwdLayout {
+    static constexpr int NUM_A = 1, NF = 1, NI = 0;
+    static constexpr bool HAS_P = false;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static void update4(float* f, int*, float, const float* a, const float*, const float* b, int,
+                                   const TileParams& P) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f[0] += ex2_approx(P.p * lg2_approx(fabsf(a[k] - b[k])));
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        P.out_f0[out_offset(P.out, m, n, g)] = powf(fmaxf(f[0], kUnderflow), 1.0f / P.p);
+    }
+};
+
+// sum of (|t| / M)^p with a per-output normaliser M read from P.pres (layout of the output);
+// resident value = -p lg2 M.   y = M (sum + (1e-10 / M)^p)^(1/p)
+struct FwdPowNorm : FwdLayout {
+    static constexpr int NUM_A = 1, NF = 1, NI = 0;
+    static constexpr bool HAS_P = true;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static void update4(float* f, int*, float cm, const float* a, const float*, const float* b, int,
+                                   const TileParams& P) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f[0] += ex2_approx(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm));
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
+        return -P.p * log2f(P.pres.ptr[out_offset(P.out, m, n, g)]);
+    }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        const long long off = out_offset(P.out, m, n, g);
+        const float M = P.pres.ptr[off];
+        const float s = f[0] + exp2f(P.p * (log2f(kEps) - log2f(M)));
+        P.out_f0[off] = M * powf(s, 1.0f / P.p);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// p = inf, forward.  The running maximum is exact whatever the evaluation order.  With POS the kernel
+// also records in which group of 4 consecutive channels the maximum first strictly increased to its
+// final value; finalize rescans those 4 channels for the first one equal to the maximum, which is the
+// index a strictly-greater scan in ascending channel order ends with.
+// ------------------------------------------------------------------------------------------------
+template <bool POS>
+struct FwdInf : FwdLayout {
+    static constexpr int NUM_A = 1, NF = 1, NI = POS ? 1 : 0;
+    static constexpr bool HAS_P = false;
+    __device__ static void init(float* f, int* n) {
+        f[0] = kEps;
+        if (POS) n[0] = -1;
+    }
+    __device__ static void update4(float* f, int* n, float, const float* a, const float*, const float* b,
+                                   int chunk, const TileParams&) {
+        const float mm = max4abs(a[0] - b[0], a[1] - b[1], a[2] - b[2], a[3] - b[3]);
+        if (POS) {
+            if (mm > f[0]) {
+                f[0] = mm;
+                n[0] = chunk;
+            }
+        } else {
+            f[0] = fmaxf(f[0], mm);
+        }
+    }
+    __device__ static void combine(float* f, int* n, const float* pf, const int* pn) {
+        if (POS) {
+            if (pf[0] > f[0]) {
+                f[0] = pf[0];
+                n[0] = pn[0];
+            }
+        } else {
+            f[0] = fmaxf(f[0], pf[0]);
+        }
+    }
+    __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
+    __device__ static void finalize(const float* f, const int* nn, float, int m, int n, int g, const TileParams& P) {
+        const long long off = out_offset(P.out, m, n, g);
+        P.out_f0[off] = f[0];
+        if (POS) {
+            int pos = 0;
+            if (nn[0] >= 0) {
+                const float* ar = P.a0.ptr + m * P.a0.stride_row + g * P.a0.stride_group;
+                const float* br = P.b.ptr + n * P.b.stride_row + g * P.b.stride_group;
+                for (int kk = 0; kk < 4; ++kk) {
+                    const int k = nn[0] * 4 + kk;
+                    if (k >= P.K) break;
+                    const float t = ar[k] - br[k];
+                    if (fabsf(t) == f[0]) {
+                        pos = k | (t >= 0.0f ? 0 : kSignBit);
+                        break;
+                    }
+                }
+            }
+            P.out_i0[off] = pos;
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// p = inf interval bounds, forward.  A operands are the (sanitised) lower and upper inputs; with
+// t1 = w - lower, t2 = upper - w the lower bound is -min(-1e-10, min_c min(t1, t2)) and the upper
+// bound max(1e-10, max_c max(t1, t2)).  FwdBound produces both values.  The variant with argmin /
+// argmax indices would need four accumulators per output, so it runs as two passes of FwdBoundPos
+// (one per bound), each tracking the 4-channel group like FwdInf<true>.
+// ------------------------------------------------------------------------------------------------
+struct FwdBound : FwdLayout {
+    static constexpr int NUM_A = 2, NF = 2, NI = 0;
+    static constexpr bool HAS_P = false;
+    __device__ static void init(float* f, int*) {
+        f[0] = -kEps;
+        f[1] = kEps;
+    }
+    __device__ static void update4(float* f, int*, float, const float* lo, const float* up, const float* w, int,
+                                   const TileParams&) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float t1 = w[k] - lo[k], t2 = up[k] - w[k];
+            f[0] = fminf(fminf(f[0], t1), t2);
+            f[1] = fmaxf(fmaxf(f[1], t1), t2);
+        }
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) {
+        f[0] = fminf(f[0], pf[0]);
+        f[1] = fmaxf(f[1], pf[1]);
+    }
+    __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        const long long off = out_offset(P.out, m, n, g);
+        P.out_f0[off] = -f[0];
+        P.out_f1[off] = f[1];
+    }
+};
+
+template <bool UPPER>
+struct FwdBoundPos : FwdLayout {
+    static constexpr int NUM_A = 2, NF = 1, NI = 1;
+    static constexpr bool HAS_P = false;
+    __device__ static void init(float* f, int* n) {
+        f[0] = UPPER ? kEps : -kEps;
+        n[0] = -1;
+    }
+    __device__ static float pick(float t1, float t2) { return UPPER ? fmaxf(t1, t2) : fminf(t1, t2); }
+    __device__ static void update4(float* f, int* n, float, const float* lo, const float* up, const float* w,
+                                   int chunk, const TileParams&) {
+        float e = pick(w[0] - lo[0], up[0] - w[0]);
+#pragma unroll
+        for (int k = 1; k < 4; ++k) {
+            const float t1 = w[k] - lo[k], t2 = up[k] - w[k];
+            e = UPPER ? fmaxf(fmaxf(e, t1), t2) : fminf(fminf(e, t1), t2);
+        }
+        if (UPPER ? (e > f[0]) : (e < f[0])) {
+            f[0] = e;
+            n[0] = chunk;
+        }
+    }
+    __device__ static void combine(float* f, int* n, const float* pf, const int* pn) {
+        if (UPPER ? (pf[0] > f[0]) : (pf[0] < f[0])) {
+            f[0] = pf[0];
+            n[0] = pn[0];
+        }
+    }
+    __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
+    __device__ static void finalize(const float* f, const int* nn, float, int m, int n, int g, const TileParams& P) {
+        const long long off = out_offset(P.out, m, n, g);
+        int pos = UPPER ? 0 : kNoGrad;
+        if (nn[0] >= 0) {
+            const float* lr = P.a0.ptr + m * P.a0.stride_row + g * P.a0.stride_group;
+            const float* ur = P.a1.ptr + m * P.a1.stride_row + g * P.a1.stride_group;
+            const float* wr = P.b.ptr + n * P.b.stride_row + g * P.b.stride_group;
+            for (int kk = 0; kk < 4; ++kk) {
+                const int k = nn[0] * 4 + kk;
+                if (k >= P.K) break;
+                const float t1 = wr[k] - lr[k], t2 = ur[k] - wr[k];
+                if (pick(t1, t2) == f[0]) {
+                    pos = k | (t1 <= t2 ? 0 : kSignBit);
+                    break;
+                }
+            }
+        }
+        if (UPPER) {
+            P.out_f1[off] = f[0];
+            P.out_i1[off] = pos;
+        } else {
+            P.out_f0[off] = -f[0];
+            P.out_i0[off] = pos;
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// Finite p, backward.  One engine problem per gradient:
+//   grad_x: out (m = (b, hw), n = c), k = o;  A = coefficient [m][k] (RowMajor), B = w [k][n] (KMajor),
+//           resident = x[m][n], t = resident - B
+//   grad_w: out (m = o, n = c), k = (b, hw);  A = coefficient [k][m] (KMajor),  B = x [k][n] (KMajor),
+//           resident = w[m][n], t = B - resident, result negated
+// Integer p - 1: coefficient = g / y^(p-1), term = coefficient * sgn(t) |t|^(p-1).
+// General p:     coefficients r = 1 / y and g, term = g * sgn(t) * 2^((p-1) lg2(|t| r)).
+// ------------------------------------------------------------------------------------------------
+template <bool WEIGHT>
+struct BwdLayout {
+    static constexpr Layout LA = WEIGHT ? Layout::KMajor : Layout::RowMajor;
+    static constexpr Layout LB = Layout::KMajor;
+    static constexpr bool HAS_P = true;
+    __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
+        return P.pres.ptr[n + m * P.pres.stride_row + g * P.pres.stride_group];
+    }
+    __device__ static float diff(float pres, float b) { return WEIGHT ? b - pres : pres - b; }
+    __device__ static void store(float v, int m, int n, int g, const TileParams& P) {
+        P.out_f0[out_offset(P.out, m, n, g)] = WEIGHT ? -v : v;
+    }
+};
+
+template <int IQ, bool WEIGHT>
+struct BwdPowInt : BwdLayout<WEIGHT> {
+    using L = BwdLayout<WEIGHT>;
+    static constexpr int NUM_A = 1, NF = 1, NI = 0;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static void update4(float* f, int*, float pres, const float* c, const float*, const float* b, int,
+                                   const TileParams&) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f[0] = fmaf(c[k], signed_pow<IQ>(L::diff(pres, b[k])), f[0]);
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        L::store(f[0], m, n, g, P);
+    }
+};
+
+template <bool WEIGHT>
+struct BwdPowGen : BwdLayout<WEIGHT> {
+    using L = BwdLayout<WEIGHT>;
+    static constexpr int NUM_A = 2, NF = 1, NI = 0;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static void update4(float* f, int*, float pres, const float* r, const float* gr, const float* b, int,
+                                   const TileParams& P) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float t = L::diff(pres, b[k]);
+            const float v = ex2_approx(P.q * lg2_approx(fabsf(t) * r[k]));
+            f[0] = fmaf(gr[k], copysignf(v, t), f[0]);
+        }
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        L::store(f[0], m, n, g, P);
+    }
+};
+
+}  // namespace ldn

@@ -1,0 +1,186 @@
+#include "ldn_prep.cuh"
+
+namespace ldn {
+
+namespace {
+constexpr int kBlock = 256;
+inline unsigned blocks_for(long long n) {
+    long long b = (n + kBlock - 1) / kBlock;
+    if (b < 1) b = 1;
+    if (b > 1184 * 8) b = 1184 * 8;  // grid-stride beyond this
+    return static_cast<unsigned>(b);
+}
+
+// index helpers -------------------------------------------------------------------------------
+// canonical arrays are [g][m][pitch]; thread index runs over (g, m, c) with c fastest
+struct CanonIdx {
+    int g, c;
+    long long m;
+};
+__device__ __forceinline__ CanonIdx canon_idx(long long i, int inner, long long M) {
+    CanonIdx r;
+    r.c = static_cast<int>(i % inner);
+    const long long t = i / inner;
+    r.m = t % M;
+    r.g = static_cast<int>(t / M);
+    return r;
+}
+
+__global__ void canon_x_kernel(const float* __restrict__ x, float* __restrict__ xc, Shape s, int pitch) {
+    const long long total = static_cast<long long>(s.G) * s.M * s.CIg;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const CanonIdx q = canon_idx(i, s.CIg, s.M);
+        const long long b = q.m / s.HW, hw = q.m % s.HW;
+        xc[(static_cast<long long>(q.g) * s.M + q.m) * pitch + q.c] = x[((b * s.G + q.g) * s.CIg + q.c) * s.HW + hw];
+    }
+}
+
+__global__ void canon_bounds_kernel(const float* __restrict__ xl, const float* __restrict__ xu, float* __restrict__ lc,
+                                    float* __restrict__ uc, Shape s, int pitch) {
+    const long long total = static_cast<long long>(s.G) * s.M * s.CIg;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const CanonIdx q = canon_idx(i, s.CIg, s.M);
+        const long long b = q.m / s.HW, hw = q.m % s.HW;
+        const long long src = ((b * s.G + q.g) * s.CIg + q.c) * s.HW + hw;
+        float lo = xl[src], up = xu[src];
+        if (lo > up) lo = up = (lo + up) * 0.5f;
+        const long long dst = (static_cast<long long>(q.g) * s.M + q.m) * pitch + q.c;
+        lc[dst] = lo;
+        uc[dst] = up;
+    }
+}
+
+__global__ void canon_w_kernel(const float* __restrict__ w, float* __restrict__ wc, Shape s, int pitch) {
+    const long long total = static_cast<long long>(s.CO) * s.CIg;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / s.CIg;
+        const int c = static_cast<int>(i - row * s.CIg);
+        wc[row * pitch + c] = w[i];
+    }
+}
+
+// thread index runs over (g, m, o) with o fastest; source offset in output layout
+__device__ __forceinline__ long long y_offset(const Shape& s, const CanonIdx& q) {
+    const long long b = q.m / s.HW, hw = q.m % s.HW;
+    return ((b * s.G + q.g) * s.COg + q.c) * s.HW + hw;
+}
+
+__global__ void coef_int_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ coef,
+                                Shape s, int pitch, int iq) {
+    const long long total = static_cast<long long>(s.G) * s.M * s.COg;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const CanonIdx q = canon_idx(i, s.COg, s.M);
+        const long long src = y_offset(s, q);
+        const float r = 1.0f / y[src];
+        float v = go[src];
+        for (int k = 0; k < iq; ++k) v *= r;
+        coef[(static_cast<long long>(q.g) * s.M + q.m) * pitch + q.c] = v;
+    }
+}
+
+__global__ void coef_gen_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ rinv,
+                                float* __restrict__ gcp, Shape s, int pitch) {
+    const long long total = static_cast<long long>(s.G) * s.M * s.COg;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const CanonIdx q = canon_idx(i, s.COg, s.M);
+        const long long src = y_offset(s, q);
+        const long long dst = (static_cast<long long>(q.g) * s.M + q.m) * pitch + q.c;
+        rinv[dst] = 1.0f / y[src];
+        gcp[dst] = go[src];
+    }
+}
+
+// One thread per output element, in output-layout order (coalesced reads of go / pos).
+__global__ void inf_scatter_kernel(const float* __restrict__ go, const int* __restrict__ pos, float* gx, float* gw,
+                                   Shape s) {
+    const long long total = static_cast<long long>(s.B) * s.CO * s.HW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int hw = static_cast<int>(i % s.HW);
+        const long long t = i / s.HW;
+        const int o = static_cast<int>(t % s.COg);
+        const long long t2 = t / s.COg;
+        const int g = static_cast<int>(t2 % s.G);
+        const long long b = t2 / s.G;
+        const int ps = pos[i];
+        const int idx = ps & 0x7fffffff;
+        const float v = ps >= 0 ? go[i] : -go[i];
+        if (gx) atomicAdd(&gx[((b * s.G + g) * s.CIg + idx) * s.HW + hw], v);
+        if (gw) atomicAdd(&gw[(static_cast<long long>(g) * s.COg + o) * s.CIg + idx], -v);
+    }
+}
+
+__global__ void bound_scatter_kernel(const float* __restrict__ gol, const float* __restrict__ gou,
+                                     const int* __restrict__ posl, const int* __restrict__ posu, float* gxl, float* gxu,
+                                     float* gw, Shape s) {
+    const long long total = static_cast<long long>(s.B) * s.CO * s.HW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int hw = static_cast<int>(i % s.HW);
+        const long long t = i / s.HW;
+        const int o = static_cast<int>(t % s.COg);
+        const long long t2 = t / s.COg;
+        const int g = static_cast<int>(t2 % s.G);
+        const long long b = t2 / s.G;
+        const int pl = posl[i], pu = posu[i];
+        const int il = pl & 0x7fffffff, iu = pu & 0x7fffffff;
+        const float vl = pl >= 0 ? gol[i] : -gol[i];
+        const float vu = pu >= 0 ? gou[i] : -gou[i];
+        const long long xrow = ((b * s.G + g) * s.CIg) * (long long)s.HW + hw;
+        const long long wrow = (static_cast<long long>(g) * s.COg + o) * s.CIg;
+        if (pl != static_cast<int>(0xffffffffu)) {
+            float* dst = pl >= 0 ? gxl : gxu;
+            atomicAdd(&dst[xrow + static_cast<long long>(il) * s.HW], vl);
+            if (gw) atomicAdd(&gw[wrow + il], -vl);
+        }
+        float* dst = pu >= 0 ? gxu : gxl;
+        atomicAdd(&dst[xrow + static_cast<long long>(iu) * s.HW], vu);
+        if (gw) atomicAdd(&gw[wrow + iu], -vu);
+    }
+}
+}  // namespace
+
+#define LDN_LAUNCH_RET() return cuda_status(cudaGetLastError())
+
+int launch_canon_x(const float* x, float* xc, const Shape& s, int pitch, cudaStream_t st) {
+    canon_x_kernel<<<blocks_for((long long)s.G * s.M * s.CIg), kBlock, 0, st>>>(x, xc, s, pitch);
+    LDN_LAUNCH_RET();
+}
+int launch_canon_bounds(const float* xl, const float* xu, float* lc, float* uc, const Shape& s, int pitch,
+                        cudaStream_t st) {
+    canon_bounds_kernel<<<blocks_for((long long)s.G * s.M * s.CIg), kBlock, 0, st>>>(xl, xu, lc, uc, s, pitch);
+    LDN_LAUNCH_RET();
+}
+int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStream_t st) {
+    canon_w_kernel<<<blocks_for((long long)s.CO * s.CIg), kBlock, 0, st>>>(w, wc, s, pitch);
+    LDN_LAUNCH_RET();
+}
+int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, cudaStream_t st) {
+    coef_int_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, coef, s, pitch, iq);
+    LDN_LAUNCH_RET();
+}
+int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
+                    cudaStream_t st) {
+    coef_gen_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, rinv, gcp, s, pitch);
+    LDN_LAUNCH_RET();
+}
+
+int launch_inf_scatter(const float* go, const int* pos, float* gx, float* gw, const Shape& s, cudaStream_t st) {
+    cudaError_t e = cudaSuccess;
+    if (gx) e = cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)s.B * s.CI * s.HW, st);
+    if (e == cudaSuccess && gw) e = cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)s.CO * s.CIg, st);
+    if (e != cudaSuccess) return cuda_status(e);
+    inf_scatter_kernel<<<blocks_for((long long)s.B * s.CO * s.HW), kBlock, 0, st>>>(go, pos, gx, gw, s);
+    LDN_LAUNCH_RET();
+}
+
+int launch_bound_scatter(const float* gol, const float* gou, const int* posl, const int* posu, float* gxl, float* gxu,
+                         float* gw, const Shape& s, cudaStream_t st) {
+    cudaError_t e = cudaMemsetAsync(gxl, 0, sizeof(float) * (size_t)s.B * s.CI * s.HW, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(gxu, 0, sizeof(float) * (size_t)s.B * s.CI * s.HW, st);
+    if (e == cudaSuccess && gw) e = cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)s.CO * s.CIg, st);
+    if (e != cudaSuccess) return cuda_status(e);
+    bound_scatter_kernel<<<blocks_for((long long)s.B * s.CO * s.HW), kBlock, 0, st>>>(gol, gou, posl, posu, gxl, gxu,
+                                                                                     gw, s);
+    LDN_LAUNCH_RET();
+}
+
+}  // namespace ldn

@@ -1,0 +1,32 @@
+// Memory-bound helper kernels: canonical operand copies, backward coefficients, p = inf scatters.
+#pragma once
+#include "ldn_common.cuh"
+
+namespace ldn {
+
+struct Shape {
+    int B, CO, CI, G, HW;
+    int CIg, COg;
+    long long M;  // B * HW
+};
+
+// xc[g][m][pitch] <- x[((b G + g) CIg + c) HW + hw],  m = b HW + hw
+int launch_canon_x(const float* x, float* xc, const Shape& s, int pitch, cudaStream_t st);
+// same for a (lower, upper) pair; elements with lower > upper are replaced by their midpoint
+int launch_canon_bounds(const float* xl, const float* xu, float* lc, float* uc, const Shape& s, int pitch,
+                        cudaStream_t st);
+// wc[g][o][pitch] <- w[(g COg + o) CIg + c]
+int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStream_t st);
+// integer p - 1 = iq:  coef[g][m][pitch] <- go / y^iq   (go, y in output layout)
+int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, cudaStream_t st);
+// general p: rinv[g][m][pitch] <- 1 / y, gcp[g][m][pitch] <- go
+int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
+                    cudaStream_t st);
+
+// p = inf backward: gx[b, idx] += v, gw[o, idx] -= v with v = pos >= 0 ? go : -go.  gx / gw may be null.
+int launch_inf_scatter(const float* go, const int* pos, float* gx, float* gw, const Shape& s, cudaStream_t st);
+// interval-bound backward (see ldn_bound_inf_dist_backward_input_weight).  gw may be null.
+int launch_bound_scatter(const float* gol, const float* gou, const int* posl, const int* posu, float* gxl, float* gxu,
+                         float* gw, const Shape& s, cudaStream_t st);
+
+}  // namespace ldn
