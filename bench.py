@@ -1,0 +1,525 @@
+#!/usr/bin/env python
+"""Benchmark of the L_p-distance hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--p 8|37.5|inf] [--impl ours|reference|reference-cuda]
+
+One "step" is one pass of the hot path over one batch: forward, grad_input and grad_weight of a single
+norm_dist layer at the headline shape 512 x 3072 -> 5120 (per rank), p = 8 by default.  With N > 1 ranks
+every rank works on its own batch (weak scaling, the batch dimension shards without communication) and
+the step ends with the NCCL all-reduce (mean) of grad_weight, the one exchange data-parallel training
+has.  The metric is pairs per second, a pair being one (sample, output, input) interaction; a step visits
+every pair three times (forward, grad_input, grad_weight).
+
+`value` is measured with all inputs resident in HBM; `e2e` goes through the public autograd API
+(`l_inf_dist_net_v2_b200.norm_dist`) with the batch and the upstream gradient copied from pinned host
+memory and the layer output copied back inside the timed region.  `--impl reference` times the
+reference's CPU torch path (restated in oracle/torch_port.py) on the host cores on a bounded sample of
+the same workload; `--impl reference-cuda` (extra) times the reference's own CUDA kernels recompiled for
+sm_100a (oracle/_ref) on the same inputs.
+"""
+import argparse
+import ctypes
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "norm_dist_fwd_bwd_pairs_per_s"
+UNIT = "Gpair/s"
+SM_LANES = 128  # FP32 lanes per SM
+MUFU_LANES = 16
+
+# algorithmic FP32 lane-instructions per pair (an FMA counts once): forward / grad_input / grad_weight
+SLOTS = {"8": (4, 6, 6), "inf": (2, None, None), "general": (6, 6, 6)}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
+    ap.add_argument("--p", default="8")
+    ap.add_argument("--batch", type=int, default=512)
+    ap.add_argument("--ci", type=int, default=3072)
+    ap.add_argument("--co", type=int, default=5120)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-variants", action="store_true")
+    return ap.parse_args()
+
+
+def p_value(s):
+    return math.inf if s in ("inf", "infinity") else float(s)
+
+
+def p_family(p):
+    if math.isinf(p):
+        return "inf"
+    if float(p).is_integer() and 1 <= p <= 8:
+        return "int"
+    return "general"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.samples = []
+        self.proc = None
+        self.thread = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            self.sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            self.sel = str(device_index)
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [s.strip() for s in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+                pw.append(float(s[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workload
+# ------------------------------------------------------------------------------------------------
+def make_host_inputs(args, rank):
+    """Synthetic stand-in for a CIFAR-10 batch (3 x 32 x 32 images flattened to 3072 features in [0, 1]),
+    N(0, 1) weights as the reference initialises them, N(0, 1) upstream gradient.  CPU generator: weights
+    seed 0 on every rank, data seed = rank."""
+    gw = torch.Generator().manual_seed(0)
+    w = torch.randn(args.co, args.ci, generator=gw)
+    gd = torch.Generator().manual_seed(1000 + rank)
+    x = torch.rand(args.batch, args.ci, 1, generator=gd)
+    g = torch.randn(args.batch, args.co, 1, generator=gd)
+    return x, w, g
+
+
+def event_ms_list(fn, steps, warmup, flush):
+    for _ in range(warmup):
+        flush()
+        fn()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    import l_inf_dist_net_v2_b200 as ldn
+    from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
+    from l_inf_dist_net_v2_b200._lib import lib
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    p = p_value(args.p)
+    fam = p_family(p)
+    B, CI, CO = args.batch, args.ci, args.co
+    pairs = B * CI * CO
+    xh, wh, gh = make_host_inputs(args, rank)
+    xh, gh = xh.pin_memory(), gh.pin_memory()
+    x, w, g = xh.to(dev), wh.to(dev), gh.to(dev)
+    y = torch.empty(B, CO, 1, device=dev)
+    pos = torch.empty(B, CO, 1, device=dev, dtype=torch.int32)
+    gx = torch.empty_like(x)
+    gw = torch.empty_like(w)
+    yh = torch.empty(B, CO, 1).pin_memory()
+    flush_buf = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+
+    def flush():
+        flush_buf.zero_()
+
+    def fwd(pp=p):
+        if math.isinf(pp):
+            C.inf_dist_forward(x, w, y, pos, 1)
+        else:
+            C.norm_dist_forward(x, w, y, 1, pp)
+
+    def bwd_x(pp=p):
+        if math.isinf(pp):
+            C.inf_dist_backward_input(g, pos, gx, 1)
+        else:
+            C.norm_dist_backward_input(g, x, w, y, gx, 1, pp)
+
+    def bwd_w(pp=p):
+        if math.isinf(pp):
+            C.inf_dist_backward_input_weight(g, pos, None, gw, 1)
+        else:
+            C.norm_dist_backward_input_weight(g, x, w, y, None, gw, 1, pp)
+
+    def bwd(pp=p):
+        if math.isinf(pp):
+            C.inf_dist_backward_input_weight(g, pos, gx, gw, 1)
+        else:
+            C.norm_dist_backward_input_weight(g, x, w, y, gx, gw, 1, pp)
+
+    def step():
+        fwd()
+        bwd()
+        if world > 1:
+            dist.all_reduce(gw)
+            gw.div_(world)
+
+    # public-API step with host buffers
+    w_param = w.clone().requires_grad_()
+    x_dev = torch.empty_like(x)
+    g_dev = torch.empty_like(g)
+
+    def step_e2e():
+        x_dev.copy_(xh, non_blocking=True)
+        g_dev.copy_(gh, non_blocking=True)
+        xin = x_dev.detach().requires_grad_()
+        w_param.grad = None
+        out = ldn.norm_dist(xin, w_param, p)
+        out.backward(g_dev)
+        if world > 1:
+            dist.all_reduce(w_param.grad)
+            w_param.grad.div_(world)
+        yh.copy_(out.detach(), non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    # ---- timed region: device-resident ----------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    for _ in range(max(args.warmup, 3)):
+        flush()
+        step()
+    torch.cuda.synchronize()
+    barrier()
+    sampler.start()
+    launches0 = lib.ldn_kernel_launches()
+    torch.cuda.synchronize()
+    t_wall0 = time.perf_counter()
+    ms = event_ms_list(step, args.steps, 0, flush)
+    torch.cuda.synchronize()
+    barrier()
+    t_wall1 = time.perf_counter()
+    launches = int(lib.ldn_kernel_launches() - launches0)
+    clocks = sampler.stop()
+    total_ms = sum(ms)
+    # ---- timed region: end to end ----------------------------------------------------------------
+    barrier()
+    ms_e2e = event_ms_list(step_e2e, args.steps, max(args.warmup, 3), flush)
+    torch.cuda.synchronize()
+    barrier()
+    total_e2e = sum(ms_e2e)
+    C.check_status()
+
+    if world > 1:
+        t = torch.tensor([total_ms, total_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, total_e2e = float(t[0]), float(t[1])
+
+    if rank != 0:
+        return None
+
+    value = world * pairs * args.steps / (total_ms * 1e-3) / 1e9
+    e2e_value = world * pairs * args.steps / (total_e2e * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(total_ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"norm_dist layer fwd+bwd {B}x{CI}->{CO} per rank, p={args.p}, G=1, HW=1",
+                   "p": args.p, "batch_per_rank": B, "in_features": CI, "out_features": CO,
+                   "pairs_per_step_per_rank": pairs, "passes_per_pair": 3,
+                   "exchange": "NCCL all-reduce(mean) of grad_weight" if world > 1 else "none",
+                   "l2": "256 MiB buffer overwritten before every timed step"},
+        "samples_per_s": round(world * B * args.steps / (total_ms * 1e-3), 1),
+        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "ms_per_step": round(total_e2e / args.steps, 4),
+                "h2d_bytes_per_step": xh.numel() * 4 + gh.numel() * 4, "d2h_bytes_per_step": yh.numel() * 4,
+                "api": "l_inf_dist_net_v2_b200.norm_dist + autograd backward"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "wall_s_timed_region": round(t_wall1 - t_wall0, 3),
+    }
+
+    # ---- per-kernel rooflines (rank 0) ------------------------------------------------------------
+    props = torch.cuda.get_device_properties(dev)
+    sms = props.multi_processor_count
+    max_mhz = clocks.get("sm_max_mhz") or 1965.0
+    sink = torch.zeros(64, device=dev)
+    lane_ops = ctypes.c_ulonglong(0)
+
+    def probe(kind, iters):
+        def run():
+            lib.ldn_probe_pipe(kind, iters, sink.data_ptr(), ctypes.byref(lane_ops),
+                               torch.cuda.current_stream().cuda_stream)
+        t = min(event_ms_list(run, 5, 2, lambda: None))
+        return lane_ops.value / (t * 1e-3) / 1e12
+
+    ffma_peak = probe(0, 4000)
+    mufu_peak = probe(1, 1000)
+    nominal_fp32 = sms * SM_LANES * max_mhz * 1e6 / 1e12
+    nominal_mufu = sms * MUFU_LANES * max_mhz * 1e6 / 1e12
+
+    def kernel_rows(pp, label, steps):
+        fam_ = p_family(pp)
+        s_f, s_x, s_w = SLOTS["inf" if fam_ == "inf" else ("8" if fam_ == "int" else "general")]
+        rows = []
+        fwd(pp)
+        for name, fn, slots in (("forward", lambda: fwd(pp), s_f), ("grad_input", lambda: bwd_x(pp), s_x),
+                                ("grad_weight", lambda: bwd_w(pp), s_w)):
+            t = statistics.median(event_ms_list(fn, steps, 3, flush))
+            row = {"p": label, "kernel": name, "ms": round(t, 4), "gpair_per_s": round(pairs / (t * 1e-3) / 1e9, 1)}
+            if fam_ == "inf" and name != "forward":
+                # scatter kernels: HBM-bound.  bytes: g + pos reads, zero-fill of the gradient, one 8-byte
+                # read-modify-write per scattered element
+                nb = 8 * B * CO + 4 * (B * CI if name == "grad_input" else CO * CI) + 8 * B * CO
+                row.update({"bound": "hbm", "bytes": nb, "gb_per_s": round(nb / (t * 1e-3) / 1e9, 1)})
+            else:
+                ach = slots * pairs / (t * 1e-3) / 1e12
+                row.update({"bound": "fp32", "slots_per_pair": slots, "tlaneop_per_s": round(ach, 2),
+                            "frac_of_ffma_probe": round(ach / ffma_peak, 3),
+                            "frac_of_nominal": round(ach / nominal_fp32, 3)})
+                if fam_ == "general":
+                    mu = 2 * pairs / (t * 1e-3) / 1e12
+                    row.update({"mufu_top_per_s": round(mu, 3), "frac_of_mufu_probe": round(mu / mufu_peak, 3)})
+            rows.append(row)
+        return rows
+
+    rows = kernel_rows(p, args.p, max(10, args.steps))
+    dominant = max(rows, key=lambda r: r["ms"])
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    if dominant["bound"] == "fp32":
+        line["roofline"] = {
+            "bound": "fp32", "kernel": f"{dominant['kernel']} (p={args.p})", "achieved": dominant["tlaneop_per_s"],
+            "peak": round(ffma_peak, 2), "unit": "Tlaneop/s", "frac": dominant["frac_of_ffma_probe"],
+            "peak_source": "FFMA-loop probe measured in this run (MEASURED_PEAKS.json holds no FP32 figure)",
+            "peak_nominal": round(nominal_fp32, 2), "frac_of_nominal": dominant["frac_of_nominal"],
+            "slots_per_pair": dominant["slots_per_pair"], "ms": dominant["ms"], "traffic": None}
+    else:
+        line["roofline"] = {
+            "bound": "hbm", "kernel": f"{dominant['kernel']} (p={args.p})", "achieved": dominant["gb_per_s"],
+            "peak": hbm_peak, "unit": "GB/s", "frac": round(dominant["gb_per_s"] / hbm_peak, 3),
+            "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s", "ms": dominant["ms"],
+            "traffic": None}
+    line["kernels"] = rows
+    line["probes"] = {"ffma_tlaneop_per_s": round(ffma_peak, 2), "mufu_top_per_s": round(mufu_peak, 3),
+                      "nominal_fp32_tlaneop_per_s": round(nominal_fp32, 2),
+                      "nominal_mufu_top_per_s": round(nominal_mufu, 3), "sms": sms}
+    if world == 1 and not args.no_variants:
+        extra = []
+        for label in ("8", "inf", "37.5"):
+            if label != args.p:
+                extra += kernel_rows(p_value(label), label, 10)
+        line["variants"] = extra
+        fwd()
+    C.check_status()
+
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args, target_s=12.0)
+    return line
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the reference's CPU torch path (oracle/torch_port.py)
+# ------------------------------------------------------------------------------------------------
+def _cpu_sample(args, rows, cols):
+    gen = torch.Generator().manual_seed(0)
+    x = torch.rand(rows, args.ci, 1, generator=gen)
+    w = torch.randn(cols, args.ci, generator=gen)
+    g = torch.randn(rows, cols, 1, generator=gen)
+    return x, w, g
+
+
+def _cpu_step(x, w, g, p):
+    from oracle import torch_port
+    t0 = time.perf_counter()
+    torch_port.norm_dist_fwd_bwd(x, w, g, p, chunk=256)
+    return time.perf_counter() - t0
+
+
+def _size_sample(args, p, target_s):
+    """Chooses (rows, cols) of the workload so that one forward+backward takes about target_s seconds."""
+    rows = min(args.batch, 32)
+    x, w, g = _cpu_sample(args, rows, 256)
+    _cpu_step(x, w, g, p)
+    t = _cpu_step(x, w, g, p)
+    per_col = t / 256
+    cols = int(max(256, min(args.co, (target_s / per_col) // 256 * 256)))
+    return rows, cols
+
+
+def cpu_baseline(args, target_s):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    p = p_value(args.p)
+    rows, cols = _size_sample(args, p, target_s)
+    x, w, g = _cpu_sample(args, rows, cols)
+    t = _cpu_step(x, w, g, p)
+    pairs = rows * cols * args.ci
+    return {"value": round(pairs / t / 1e9, 4), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{rows} of {args.batch} batch rows x {cols} of {args.co} outputs x {args.ci} inputs, "
+                      f"forward + autograd backward, p={args.p}, {t:.1f} s",
+            "path": "oracle/torch_port.py (broadcast + vector_norm, the reference's use_custom_cuda_func=False path)"}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return None
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    p = p_value(args.p)
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    rows, cols = _size_sample(args, p, min(3.0, budget))
+    x, w, g = _cpu_sample(args, rows, cols)
+    for _ in range(args.warmup):
+        _cpu_step(x, w, g, p)
+    times = [_cpu_step(x, w, g, p) for _ in range(args.steps)]
+    pairs = rows * cols * args.ci
+    total = sum(times)
+    value = pairs * args.steps / total / 1e9
+    sample = (f"{rows} of {args.batch} batch rows x {cols} of {args.co} outputs x {args.ci} inputs per step, "
+              f"forward + autograd backward")
+    return {
+        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"norm_dist layer fwd+bwd {args.batch}x{args.ci}->{args.co} per rank, p={args.p}, "
+                               f"G=1, HW=1", "p": args.p, "batch_per_rank": args.batch, "in_features": args.ci,
+                   "out_features": args.co, "sample": sample},
+        "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def run_reference_cuda(args, rank, local_rank):
+    """Extra arm: the reference's own CUDA kernels (oracle/_ref, recompiled for sm_100a) on the same step."""
+    if rank != 0:
+        return None
+    from oracle.build import REF_SO
+    if not os.path.exists(REF_SO):
+        return {"impl": "reference-cuda", "unavailable": "oracle/_ref/libldn_ref.so was not built"}
+    ref = ctypes.CDLL(REF_SO)
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    p = p_value(args.p)
+    B, CI, CO = args.batch, args.ci, args.co
+    xh, wh, gh = make_host_inputs(args, rank)
+    x, w, g = xh.to(dev), wh.to(dev), gh.to(dev)
+    y = torch.empty(B, CO, 1, device=dev)
+    pos = torch.empty(B, CO, 1, device=dev, dtype=torch.int32)
+    gx, gw = torch.empty_like(x), torch.empty_like(w)
+    flush_buf = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    dims = (B, CO, CI, 1, 1)
+
+    def fwd():
+        if math.isinf(p):
+            ref.ldn_ref_inf_dist_forward(P(x), P(w), P(y), P(pos), *dims)
+        else:
+            ref.ldn_ref_norm_dist_forward(P(x), P(w), P(y), *dims, ctypes.c_float(p))
+
+    def bwd():
+        if math.isinf(p):
+            ref.ldn_ref_inf_dist_backward_input_weight(P(g), P(pos), P(gx), P(gw), *dims)
+        else:
+            ref.ldn_ref_norm_dist_backward_input_weight(P(g), P(x), P(w), P(y), P(gx), P(gw), *dims, ctypes.c_float(p))
+
+    def step():
+        fwd()
+        bwd()
+
+    flush = flush_buf.zero_
+    ms = event_ms_list(step, args.steps, max(args.warmup, 3), flush)
+    t_f = statistics.median(event_ms_list(fwd, 10, 2, flush))
+    t_b = statistics.median(event_ms_list(bwd, 10, 2, flush))
+    pairs = B * CI * CO
+    return {"impl": "reference-cuda", "metric": METRIC, "unit": UNIT,
+            "value": round(pairs * args.steps / (sum(ms) * 1e-3) / 1e9, 2), "ms_per_step": round(sum(ms) / args.steps, 4),
+            "forward_ms": round(t_f, 4), "backward_ms": round(t_b, 4), "n_gpus": 1, "steps": args.steps,
+            "config": {"workload": f"norm_dist layer fwd+bwd {B}x{CI}->{CO}, p={args.p}, reference CUDA kernels "
+                                   f"recompiled for sm_100a"}}
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        line = run_reference(args, rank)
+    elif args.impl == "reference-cuda":
+        line = run_reference_cuda(args, rank, local_rank)
+    else:
+        if world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        line = run_ours(args, rank, world, local_rank)
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

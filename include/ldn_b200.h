@@ -59,6 +59,20 @@ LDN_API int ldn_release_scratch(void);
  */
 LDN_API void ldn_set_max_ctas(int max_ctas);
 
+/*
+ * Number of kernels this library has launched in the calling process so far (all devices, all streams).
+ * No counterpart in the reference.
+ */
+LDN_API unsigned long long ldn_kernel_launches(void);
+
+/*
+ * Pipe-throughput probe for roofline denominators (no counterpart in the reference).  kind 0 runs a loop
+ * of independent FFMA chains, kind 1 a loop of independent ex2(lg2(x)) chains, `iters` iterations, on
+ * 8 CTAs of 256 threads per SM.  *lane_ops receives the number of lane operations the launch executes
+ * (FFMAs, respectively MUFU operations); the caller times the launch.  sink: one device float.
+ */
+LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream);
+
 /* ---- finite p ------------------------------------------------------------------------------- */
 
 /*

@@ -1,6 +1,6 @@
 """sm_100a (B200) implementation of the L_p-distance operator family of zbh2047/L_inf-dist-net-v2.
 
-Importing this package loads libldn_b200.so (built in-tree by `python -m l_inf_dist_net_v2_b200.build`);
+Importing this package loads libldn_b200.so (built in-tree by `python l_inf_dist_net_v2_b200/build.py`);
 the import fails if the library is missing -- there is no CPU or pure-PyTorch path.
 """
 from . import norm_dist_cuda  # noqa: F401  (loads the native library)

@@ -33,8 +33,9 @@ SIGNATURES = {
                                                 [_c_float_p, _c_float_p, _c_float_p, _s],
     "ldn_check_status": [_s],
     "ldn_release_scratch": [],
+    "ldn_probe_pipe": [_i, _i, _c_float_p, ctypes.c_void_p, _s],
 }
-OTHER_SYMBOLS = ["ldn_status_string", "ldn_version", "ldn_set_max_ctas"]
+OTHER_SYMBOLS = ["ldn_status_string", "ldn_version", "ldn_set_max_ctas", "ldn_kernel_launches"]
 
 
 class LdnError(RuntimeError):
@@ -44,7 +45,7 @@ class LdnError(RuntimeError):
 def load(path=LIB_PATH):
     if not os.path.exists(path):
         raise ImportError(
-            f"{path} is missing: build it with `python -m l_inf_dist_net_v2_b200.build` "
+            f"{path} is missing: build it with `python l_inf_dist_net_v2_b200/build.py` "
             "(needs nvcc; there is no CPU or PyTorch fallback for these operators)")
     lib = ctypes.CDLL(path)
     for name, args in SIGNATURES.items():
@@ -57,6 +58,8 @@ def load(path=LIB_PATH):
     lib.ldn_version.restype = ctypes.c_char_p
     lib.ldn_set_max_ctas.argtypes = [ctypes.c_int]
     lib.ldn_set_max_ctas.restype = None
+    lib.ldn_kernel_launches.argtypes = []
+    lib.ldn_kernel_launches.restype = ctypes.c_ulonglong
     return lib
 
 

@@ -1,6 +1,8 @@
 """Builds libldn_b200.so (sm_100a only) in-tree with nvcc.
 
-    python -m l_inf_dist_net_v2_b200.build [--force] [--verbose]
+    python l_inf_dist_net_v2_b200/build.py [--force] [--verbose]
+
+(run it as a script: importing the package needs the library this script produces)
 
 Each translation unit is compiled on its own (in parallel) and the objects are linked into
 l_inf_dist_net_v2_b200/libldn_b200.so.  nvcc cross-compiles without a GPU.

@@ -175,6 +175,9 @@ inline size_t pad256(size_t bytes) { return (bytes + 255) & ~size_t(255); }
 int make_tensor_map(CUtensorMap* map, const float* base, const unsigned long long dims[3],
                     const unsigned long long strides_elems[2], const unsigned box[3], bool swizzle128);
 
+// host-side launch counter (ldn_diag.cu)
+void count_launches(int n);
+
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? kOk : kCudaBase + static_cast<int>(e); }
 
 }  // namespace ldn

@@ -1,0 +1,66 @@
+// Diagnostics exported next to the operators: a host-side count of kernel launches and two
+// pipe-throughput probes (dependent-chain-free FFMA and MUFU loops) that give the measured
+// denominators for the compute rooflines.
+#include <atomic>
+
+#include "ldn_b200.h"
+#include "ldn_common.cuh"
+
+namespace ldn {
+std::atomic<unsigned long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+
+namespace {
+constexpr int kProbeThreads = 256;
+constexpr int kProbeIlp = 16;
+
+// kind 0: 16 independent FFMA chains per thread.  kind 1: 16 independent ex2(lg2(x)) chains (2 MUFU each).
+template <int KIND>
+__global__ void __launch_bounds__(kProbeThreads) probe_kernel(int iters, float seed, float* sink) {
+    float v[kProbeIlp];
+#pragma unroll
+    for (int i = 0; i < kProbeIlp; ++i) v[i] = seed + 0.001f * (threadIdx.x + i);
+    const float a = 0.999f, b = 0.0005f;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < kProbeIlp; ++i) {
+            if (KIND == 0) {
+                v[i] = fmaf(v[i], a, b);
+            } else {
+                float l, e;
+                asm volatile("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(v[i]));
+                asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(l));
+                v[i] = e;
+            }
+        }
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kProbeIlp; ++i) s += v[i];
+    if (s == 12345.678f) sink[0] = s;  // keeps the loop alive, practically never true
+}
+}  // namespace
+}  // namespace ldn
+
+using namespace ldn;
+
+extern "C" {
+
+LDN_API unsigned long long ldn_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
+
+LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream) {
+    if (!sink || !lane_ops || iters <= 0 || (kind != 0 && kind != 1)) return kBadArgument;
+    const DeviceCtx* ctx;
+    int r = get_device_ctx(&ctx);
+    if (r != kOk) return r;
+    const int blocks = ctx->sm_count * 8;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (kind == 0) probe_kernel<0><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
+    else probe_kernel<1><<<blocks, kProbeThreads, 0, st>>>(iters, 1.5f, sink);
+    // kind 0: one FFMA per chain step; kind 1: two MUFU operations per chain step
+    *lane_ops = static_cast<unsigned long long>(blocks) * kProbeThreads * iters * kProbeIlp * (kind == 0 ? 1 : 2);
+    count_launches(1);
+    return cuda_status(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -138,7 +138,11 @@ __global__ void bound_scatter_kernel(const float* __restrict__ gol, const float*
 }
 }  // namespace
 
-#define LDN_LAUNCH_RET() return cuda_status(cudaGetLastError())
+#define LDN_LAUNCH_RET() \
+    do {                  \
+        count_launches(1); \
+        return cuda_status(cudaGetLastError()); \
+    } while (0)
 
 int launch_canon_x(const float* x, float* xc, const Shape& s, int pitch, cudaStream_t st) {
     canon_x_kernel<<<blocks_for((long long)s.G * s.M * s.CIg), kBlock, 0, st>>>(x, xc, s, pitch);

@@ -314,11 +314,13 @@ int launch_tile(const TileLaunch& L, cudaStream_t stream) {
     tile_kernel<Op><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b, L.params);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_status(e);
+    count_launches(1);
     const long long tiles = L.params.total_iters / L.params.kt;
     // a tile can only be shared when the ranges do not fall on tile boundaries
     if (L.params.total_iters % L.grid != 0 || (L.params.total_iters / L.grid) % L.params.kt != 0) {
         tile_fixup_kernel<Op><<<static_cast<unsigned>(tiles), kThreads, 0, stream>>>(L.params, L.grid);
         e = cudaGetLastError();
+        count_launches(1);
     }
     return cuda_status(e);
 }

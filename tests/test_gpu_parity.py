@@ -368,7 +368,7 @@ def test_autograd_operator_and_modules(C):
     assert o.shape == (3, 8, 6, 6)
     un = torch.nn.functional.unfold(img, (3, 3), 1, 1, 1)
     oy, _ = oracle.inf_dist_forward(un.cpu().numpy(), conv.weight.detach().cpu().numpy(), 2, want_pos=False)
-    assert np.array_equal((o.view(3, 8, 36) - conv.bias.view(1, -1, 1)).cpu().numpy(), oy)
+    assert np.array_equal((o.view(3, 8, 36) - conv.bias.detach().view(1, -1, 1)).cpu().numpy(), oy)
     C.check_status()
 
 

@@ -114,3 +114,25 @@ def test_forward_with_max_matches_plain_forward():
     y1 = oracle.norm_dist_forward_with_max(x, w, m, 12.0, 2)
     y2 = oracle.norm_dist_forward(x, w, 12.0, 2)
     assert _rel(y1, y2) < 1e-6
+
+
+def test_torch_port_matches_reference_vectors(golden):
+    import torch
+    from oracle import torch_port
+    for key in _cases(golden):
+        G = int(golden[f"{key}/dims"][3])
+        x = torch.from_numpy(golden[f"{key}/x"])
+        w = torch.from_numpy(golden[f"{key}/w"])
+        for p in (3.0, 8.0, 37.5):
+            y = torch_port.norm_dist(x.double(), w.double(), p, G)
+            assert _rel(y.numpy(), golden[f"{key}/p{p}/y"]) < 1e-12, (key, p)
+        y = torch_port.norm_dist(x, w, float("inf"), G)
+        assert np.array_equal(y.numpy(), golden[f"{key}/inf/y"]), key
+        yL, yU = torch_port.bound_inf_dist(torch.from_numpy(golden[f"{key}/xL"]), torch.from_numpy(golden[f"{key}/xU"]), w, G)
+        assert np.array_equal(yL.numpy(), golden[f"{key}/bound/yL"]) and np.array_equal(yU.numpy(), golden[f"{key}/bound/yU"])
+        if G == 1:
+            g = torch.from_numpy(golden[f"{key}/g"])
+            y, gx, gw = torch_port.norm_dist_fwd_bwd(x.double(), w.double(), g.double(), 8.0, chunk=7)
+            assert _rel(y.numpy(), golden[f"{key}/p8.0/y"]) < 1e-12
+            assert _rel_to_max(gx.numpy(), golden[f"{key}/p8.0/gx"]) < 1e-6
+            assert _rel_to_max(gw.numpy(), golden[f"{key}/p8.0/gw"]) < 1e-6
