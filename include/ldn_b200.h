@@ -66,8 +66,16 @@ LDN_API void ldn_set_max_ctas(int max_ctas);
 LDN_API unsigned long long ldn_kernel_launches(void);
 
 /*
+ * Tracing hook (no counterpart in the reference): while a non-null device buffer is set, every CTA of every
+ * tile-engine launch writes four 64-bit words at buffer[4 * cta]: SM id, start and end time (globaltimer, ns)
+ * and its number of k-steps.  The buffer must hold 4 * (number of SMs) words; pass NULL to switch it off.
+ */
+LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer);
+
+/*
  * Pipe-throughput probe for roofline denominators (no counterpart in the reference).  kind 0 runs a loop
- * of independent FFMA chains, kind 1 a loop of independent ex2(lg2(x)) chains, `iters` iterations, on
+ * of independent FFMA chains, kind 2 the same chains issued as packed fma.rn.f32x2, kind 1 a loop of
+ * independent ex2(lg2(x)) chains, `iters` iterations, on
  * 8 CTAs of 256 threads per SM.  *lane_ops receives the number of lane operations the launch executes
  * (FFMAs, respectively MUFU operations); the caller times the launch.  sink: one device float.
  */

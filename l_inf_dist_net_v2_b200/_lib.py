@@ -35,7 +35,7 @@ SIGNATURES = {
     "ldn_release_scratch": [],
     "ldn_probe_pipe": [_i, _i, _c_float_p, ctypes.c_void_p, _s],
 }
-OTHER_SYMBOLS = ["ldn_status_string", "ldn_version", "ldn_set_max_ctas", "ldn_kernel_launches"]
+OTHER_SYMBOLS = ["ldn_status_string", "ldn_version", "ldn_set_max_ctas", "ldn_kernel_launches", "ldn_set_trace_buffer"]
 
 
 class LdnError(RuntimeError):
@@ -58,6 +58,8 @@ def load(path=LIB_PATH):
     lib.ldn_version.restype = ctypes.c_char_p
     lib.ldn_set_max_ctas.argtypes = [ctypes.c_int]
     lib.ldn_set_max_ctas.restype = None
+    lib.ldn_set_trace_buffer.argtypes = [ctypes.c_void_p]
+    lib.ldn_set_trace_buffer.restype = None
     lib.ldn_kernel_launches.argtypes = []
     lib.ldn_kernel_launches.restype = ctypes.c_ulonglong
     return lib

@@ -145,6 +145,7 @@ int fill_plan(Call& c, TileLaunch* L, long long M, int N, int K, int G, int arra
     P.partials = c.bump.take<float>(static_cast<size_t>(L->grid) * 2 * arrays * kTileElems);
     if (!P.partials) return kWorkspace;
     P.status = c.arena->status;
+    P.trace = trace_buffer();
     return kOk;
 }
 

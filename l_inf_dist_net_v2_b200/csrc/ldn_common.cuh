@@ -72,6 +72,7 @@ struct TileParams {
     float q;                    // op specific (p - 1 for backward)
     float* partials;            // stream-K scratch: [grid][2][arrays][kTileElems]
     int* status;                // device status word (0 = ok)
+    unsigned long long* trace;  // optional per-CTA trace: {sm id, start ns, end ns, iterations}; may be null
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -126,6 +127,17 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned sm_id() {
+    unsigned s;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(s));
+    return s;
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -175,7 +187,8 @@ inline size_t pad256(size_t bytes) { return (bytes + 255) & ~size_t(255); }
 int make_tensor_map(CUtensorMap* map, const float* base, const unsigned long long dims[3],
                     const unsigned long long strides_elems[2], const unsigned box[3], bool swizzle128);
 
-// host-side launch counter (ldn_diag.cu)
+// host-side launch counter and optional per-CTA trace buffer (ldn_diag.cu)
+unsigned long long* trace_buffer();
 void count_launches(int n);
 
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? kOk : kCudaBase + static_cast<int>(e); }

@@ -10,11 +10,15 @@ namespace ldn {
 std::atomic<unsigned long long> g_launches{0};
 void count_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
+unsigned long long* g_trace = nullptr;
+unsigned long long* trace_buffer() { return g_trace; }
+
 namespace {
 constexpr int kProbeThreads = 256;
 constexpr int kProbeIlp = 16;
 
 // kind 0: 16 independent FFMA chains per thread.  kind 1: 16 independent ex2(lg2(x)) chains (2 MUFU each).
+// kind 2: the FFMA chains issued as 8 packed fma.rn.f32x2 instructions.
 template <int KIND>
 __global__ void __launch_bounds__(kProbeThreads) probe_kernel(int iters, float seed, float* sink) {
     float v[kProbeIlp];
@@ -26,6 +30,13 @@ __global__ void __launch_bounds__(kProbeThreads) probe_kernel(int iters, float s
         for (int i = 0; i < kProbeIlp; ++i) {
             if (KIND == 0) {
                 v[i] = fmaf(v[i], a, b);
+            } else if (KIND == 2) {
+                // packed FP32: one instruction, two lane operations; chains pair up (i, i ^ 1)
+                if ((i & 1) == 0) {
+                    const float2 r = __ffma2_rn(make_float2(v[i], v[i + 1]), make_float2(a, a), make_float2(b, b));
+                    v[i] = r.x;
+                    v[i + 1] = r.y;
+                }
             } else {
                 float l, e;
                 asm volatile("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(v[i]));
@@ -46,19 +57,22 @@ using namespace ldn;
 
 extern "C" {
 
+LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer) { g_trace = device_buffer; }
+
 LDN_API unsigned long long ldn_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream) {
-    if (!sink || !lane_ops || iters <= 0 || (kind != 0 && kind != 1)) return kBadArgument;
+    if (!sink || !lane_ops || iters <= 0 || (kind < 0 || kind > 2)) return kBadArgument;
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
     const int blocks = ctx->sm_count * 8;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (kind == 0) probe_kernel<0><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
+    else if (kind == 2) probe_kernel<2><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
     else probe_kernel<1><<<blocks, kProbeThreads, 0, st>>>(iters, 1.5f, sink);
-    // kind 0: one FFMA per chain step; kind 1: two MUFU operations per chain step
-    *lane_ops = static_cast<unsigned long long>(blocks) * kProbeThreads * iters * kProbeIlp * (kind == 0 ? 1 : 2);
+    // kinds 0 and 2: one FMA lane operation per chain step; kind 1: two MUFU operations per chain step
+    *lane_ops = static_cast<unsigned long long>(blocks) * kProbeThreads * iters * kProbeIlp * (kind == 1 ? 2 : 1);
     count_launches(1);
     return cuda_status(cudaGetLastError());
 }

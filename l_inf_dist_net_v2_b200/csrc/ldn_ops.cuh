@@ -76,13 +76,10 @@ __device__ __forceinline__ float signed_pow(float t) {
     return (t4 * t2) * u;
 }
 
-__device__ __forceinline__ float max4abs(float a, float b, float c, float d) {
-    return fmaxf(fmaxf(fmaxf(fabsf(a), fabsf(b)), fabsf(c)), fabsf(d));
-}
-
 struct FwdLayout {
     static constexpr Layout LA = Layout::RowMajor;
     static constexpr Layout LB = Layout::RowMajor;
+    static constexpr int KSTEP = 2;  // k values per rolled inner-loop step
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -95,10 +92,11 @@ struct FwdPowInt : FwdLayout {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
-    __device__ static void update4(float* f, int*, float, const float* a, const float*, const float* b, int,
+    template <int KS>
+    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int,
                                    const TileParams&) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) f[0] = acc_abs_pow<IP>(f[0], a[k] - b[k]);
+        for (int k = 0; k < KS; ++k) f[0] = acc_abs_pow<IP>(f[0], a[k] - b[k]);
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
@@ -112,10 +110,11 @@ struct FwdPowGen : FwdLayout {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
-    __device__ static void update4(float* f, int*, float, const float* a, const float*, const float* b, int,
+    template <int KS>
+    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int,
                                    const TileParams& P) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) f[0] += ex2_approx(P.p * lg2_approx(fabsf(a[k] - b[k])));
+        for (int k = 0; k < KS; ++k) f[0] += ex2_approx(P.p * lg2_approx(fabsf(a[k] - b[k])));
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
@@ -130,10 +129,11 @@ struct FwdPowNorm : FwdLayout {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = true;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
-    __device__ static void update4(float* f, int*, float cm, const float* a, const float*, const float* b, int,
+    template <int KS>
+    __device__ static void update(float* f, int*, float cm, const float* a, const float*, const float* b, int,
                                    const TileParams& P) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) f[0] += ex2_approx(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm));
+        for (int k = 0; k < KS; ++k) f[0] += ex2_approx(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm));
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
@@ -161,9 +161,12 @@ struct FwdInf : FwdLayout {
         f[0] = kEps;
         if (POS) n[0] = -1;
     }
-    __device__ static void update4(float* f, int* n, float, const float* a, const float*, const float* b,
+    template <int KS>
+    __device__ static void update(float* f, int* n, float, const float* a, const float*, const float* b,
                                    int chunk, const TileParams&) {
-        const float mm = max4abs(a[0] - b[0], a[1] - b[1], a[2] - b[2], a[3] - b[3]);
+        float mm = fabsf(a[0] - b[0]);
+#pragma unroll
+        for (int k = 1; k < KS; ++k) mm = fmaxf(mm, fabsf(a[k] - b[k]));
         if (POS) {
             if (mm > f[0]) {
                 f[0] = mm;
@@ -221,10 +224,11 @@ struct FwdBound : FwdLayout {
         f[0] = -kEps;
         f[1] = kEps;
     }
-    __device__ static void update4(float* f, int*, float, const float* lo, const float* up, const float* w, int,
+    template <int KS>
+    __device__ static void update(float* f, int*, float, const float* lo, const float* up, const float* w, int,
                                    const TileParams&) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < KS; ++k) {
             const float t1 = w[k] - lo[k], t2 = up[k] - w[k];
             f[0] = fminf(fminf(f[0], t1), t2);
             f[1] = fmaxf(fmaxf(f[1], t1), t2);
@@ -251,11 +255,12 @@ struct FwdBoundPos : FwdLayout {
         n[0] = -1;
     }
     __device__ static float pick(float t1, float t2) { return UPPER ? fmaxf(t1, t2) : fminf(t1, t2); }
-    __device__ static void update4(float* f, int* n, float, const float* lo, const float* up, const float* w,
+    template <int KS>
+    __device__ static void update(float* f, int* n, float, const float* lo, const float* up, const float* w,
                                    int chunk, const TileParams&) {
         float e = pick(w[0] - lo[0], up[0] - w[0]);
 #pragma unroll
-        for (int k = 1; k < 4; ++k) {
+        for (int k = 1; k < KS; ++k) {
             const float t1 = w[k] - lo[k], t2 = up[k] - w[k];
             e = UPPER ? fmaxf(fmaxf(e, t1), t2) : fminf(fminf(e, t1), t2);
         }
@@ -311,6 +316,7 @@ template <bool WEIGHT>
 struct BwdLayout {
     static constexpr Layout LA = WEIGHT ? Layout::KMajor : Layout::RowMajor;
     static constexpr Layout LB = Layout::KMajor;
+    static constexpr int KSTEP = 2;
     static constexpr bool HAS_P = true;
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
         return P.pres.ptr[n + m * P.pres.stride_row + g * P.pres.stride_group];
@@ -326,10 +332,11 @@ struct BwdPowInt : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
-    __device__ static void update4(float* f, int*, float pres, const float* c, const float*, const float* b, int,
+    template <int KS>
+    __device__ static void update(float* f, int*, float pres, const float* c, const float*, const float* b, int,
                                    const TileParams&) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) f[0] = fmaf(c[k], signed_pow<IQ>(L::diff(pres, b[k])), f[0]);
+        for (int k = 0; k < KS; ++k) f[0] = fmaf(c[k], signed_pow<IQ>(L::diff(pres, b[k])), f[0]);
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
@@ -342,10 +349,11 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
-    __device__ static void update4(float* f, int*, float pres, const float* r, const float* gr, const float* b, int,
+    template <int KS>
+    __device__ static void update(float* f, int*, float pres, const float* r, const float* gr, const float* b, int,
                                    const TileParams& P) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < KS; ++k) {
             const float t = L::diff(pres, b[k]);
             const float v = ex2_approx(P.q * lg2_approx(fabsf(t) * r[k]));
             f[0] = fmaf(gr[k], copysignf(v, t), f[0]);

@@ -31,20 +31,31 @@ __device__ __forceinline__ int own_index(int t, int r) {
     return (r >> 2) * 64 + t * 4 + (r & 3);
 }
 
-// Fetch the 8 x 4 register slab (8 owned rows/cols x 4 consecutive k) of one operand tile.
-template <Layout L>
-__device__ __forceinline__ void fetch_slab(const char* tile, int t, int k4, float (&v)[8][4]) {
+// Fetch the 8 x KS register slab (8 owned rows/cols x KS consecutive k, KS in {1, 2, 4}) of one operand
+// tile for k-group `ps` (k = ps * KS .. ps * KS + KS - 1 inside the 32-wide stage).
+template <Layout L, int KS>
+__device__ __forceinline__ void fetch_slab(const char* tile, int t, int ps, float (&v)[8][KS]) {
+    static_assert(KS == 1 || KS == 2 || KS == 4, "k-step must be 1, 2 or 4");
     if (L == Layout::RowMajor) {
-        const int chunk = (k4 ^ (t & 7)) * 16;
+        const int k = ps * KS;
+        const int off = (((k >> 2) ^ (t & 7)) << 4) + ((k & 3) << 2);
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-            const float4 x = *reinterpret_cast<const float4*>(tile + (t + 16 * r) * 128 + chunk);
-            v[r][0] = x.x; v[r][1] = x.y; v[r][2] = x.z; v[r][3] = x.w;
+            const char* src = tile + (t + 16 * r) * 128 + off;
+            if constexpr (KS == 4) {
+                const float4 x = *reinterpret_cast<const float4*>(src);
+                v[r][0] = x.x; v[r][1] = x.y; v[r][2] = x.z; v[r][3] = x.w;
+            } else if constexpr (KS == 2) {
+                const float2 x = *reinterpret_cast<const float2*>(src);
+                v[r][0] = x.x; v[r][1] = x.y;
+            } else {
+                v[r][0] = *reinterpret_cast<const float*>(src);
+            }
         }
     } else {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-            const char* row = tile + (k4 * 4 + kk) * 512 + t * 16;
+        for (int kk = 0; kk < KS; ++kk) {
+            const char* row = tile + (ps * KS + kk) * 512 + t * 16;
             const float4 lo = *reinterpret_cast<const float4*>(row);
             const float4 hi = *reinterpret_cast<const float4*>(row + 256);
             v[0][kk] = lo.x; v[1][kk] = lo.y; v[2][kk] = lo.z; v[3][kk] = lo.w;
@@ -107,6 +118,8 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     const long long it1 = range_begin(P.total_iters, grid, blockIdx.x + 1);
     if (it0 >= it1) return;
     const int KT = P.kt;
+    unsigned long long t_start = 0;
+    if (P.trace && tid == 0) t_start = global_timer_ns();
 
     if (tid == 0) {
         tma_prefetch_desc(&map_a0);
@@ -188,18 +201,27 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         const char* sa0 = smem + (ls % kStages) * STAGE;
         const char* sa1 = sa0 + (NA == 2 ? kOperandTileBytes : 0);
         const char* sb = sa0 + NA * kOperandTileBytes;
-#pragma unroll 2
-        for (int k4 = 0; k4 < kTileK / 4; ++k4) {
-            float a0[8][4], a1[8][4], b[8][4];
-            fetch_slab<Op::LA>(sa0, tm, k4, a0);
-            if (NA == 2) fetch_slab<Op::LA>(sa1, tm, k4, a1);
-            fetch_slab<Op::LB>(sb, tn, k4, b);
-            const int chunk = kt * (kTileK / 4) + k4;
+        // The k-groups of a stage are walked in a rolled loop so that the loop body (64 outputs x KS k x
+        // a few FP32 instructions) stays resident in the instruction cache.  Threads with tn >= 8 visit
+        // each pair of neighbouring k-groups in swapped order (KS < 4): with the 128-byte swizzle that
+        // makes the narrower shared-memory reads of a RowMajor B tile bank-conflict free.  The order in
+        // which a thread visits k does not matter to any op (sums, exact min / max, 4-channel groups).
+        constexpr int KS = Op::KSTEP;
+        const int perm = (KS < 4) ? (tn >> 3) : 0;
+#pragma unroll 1
+        for (int ks = 0; ks < kTileK / KS; ++ks) {
+            const int ps = ks ^ perm;
+            float a0[8][KS], a1[8][KS], b[8][KS];
+            fetch_slab<Op::LA, KS>(sa0, tm, ps, a0);
+            if (NA == 2) fetch_slab<Op::LA, KS>(sa1, tm, ps, a1);
+            fetch_slab<Op::LB, KS>(sb, tn, ps, b);
+            const int chunk = kt * (kTileK / 4) + ((ps * KS) >> 2);
 #pragma unroll
             for (int i = 0; i < kRegM; ++i)
 #pragma unroll
                 for (int j = 0; j < kRegN; ++j)
-                    Op::update4(accf[i][j], acci[i][j], pres[i][j], a0[i], NA == 2 ? a1[i] : a0[i], b[j], chunk, P);
+                    Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], a0[i], NA == 2 ? a1[i] : a0[i], b[j],
+                                            chunk, P);
         }
 
         if (kt == KT - 1 || it == it1 - 1) {
@@ -229,6 +251,13 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                     }
             }
         }
+    }
+    if (P.trace && tid == 0) {
+        unsigned long long* tr = P.trace + 4ull * blockIdx.x;
+        tr[0] = sm_id();
+        tr[1] = t_start;
+        tr[2] = global_timer_ns();
+        tr[3] = static_cast<unsigned long long>(it1 - it0);
     }
 }
 
