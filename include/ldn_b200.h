@@ -172,6 +172,33 @@ LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, 
                                              int HW, float* grad_inputL, float* grad_inputU, float* grad_weight,
                                              ldn_stream_t stream);
 
+/* ---- allocation-free variant ------------------------------------------------------------------ */
+
+/*
+ * Same result as ldn_inf_dist_forward_nograd, for callers that may not allocate device memory while they
+ * run (a server whose memory was handed to its own pool at start-up, a runtime that forbids cudaMalloc after
+ * initialisation, code that is about to record its launches).  This function has no counterpart in the
+ * reference.  It calls no cudaMalloc / cudaFree and no allocating library routine: all scratch (operand
+ * copies for layouts TMA cannot read directly, the partial results of output tiles shared between CTAs) lives
+ * in one fixed 32 MiB array inside the library's device image, which every GPU that loads the library holds
+ * until the process exits.
+ *   - Limit: the call is refused with status 3 ("scratch memory could not be provided") before anything is
+ *     launched when it would need more than the fixed array.  Fully connected inputs (HW == 1) with CI/G a
+ *     multiple of 4 and 16-byte aligned pointers need 18.5 MiB whatever B, CI and CO are; other layouts add a
+ *     padded copy of the input (4 * G * B * HW * ceil4(CI/G) bytes) and, if CI/G is not a multiple of 4 or the
+ *     weight is misaligned, of the weight.
+ *   - The first call on each device looks up the array's device address (with that device current); make
+ *     that first call before any stream capture begins.
+ *   - All calls on a device share the array and it keeps whatever the last call left there.  Nothing in it
+ *     has to start at zero (every word is written before it is read within a call), but two calls whose
+ *     kernels overlap on the GPU -- different streams, or different host threads -- race on it: issue these
+ *     calls on one stream, or order them with events.
+ *   - A bounded-wait timeout inside a kernel is recorded in the first word of the array; ldn_check_status
+ *     does not report it.
+ */
+LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float* weight, int B, int CO, int CI,
+                                                int G, int HW, float* output, ldn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -485,3 +485,74 @@ LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the p = inf no-grad forward.
+//
+// Some hosts of this library must not allocate device memory once they are running: an inference
+// server that hands its whole memory budget to its own pool at start-up, a caller that is about to
+// record its launches into a CUDA graph or runs under a framework whose allocator must see every byte,
+// a safety-certified runtime that forbids cudaMalloc after initialisation.  The regular entry points
+// take their scratch from an arena that grows with cudaMalloc, so those callers get this one instead:
+// its scratch is a fixed array in the library's own device image.
+// ------------------------------------------------------------------------------------------------
+namespace ldn {
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = size_t(32) << 20;  // 32 MiB, resident on every GPU that loads the library
+constexpr size_t kNoAllocStatusBytes = 256;                // the first bytes hold the device status word
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address; the address a
+// kernel may use comes from cudaGetSymbolAddress, looked up once per device with that device current.
+char* g_noalloc_ptr[64] = {};
+
+int noalloc_scratch_address(char** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kNoDevice;
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_status(e);
+        if (!p) return kWorkspace;
+        g_noalloc_ptr[dev] = static_cast<char*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return kOk;
+}
+
+}  // namespace
+}  // namespace ldn
+
+extern "C" {
+
+LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float* weight, int B, int CO, int CI,
+                                                int G, int HW, float* output, ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r != kOk) return r;
+    if (!input || !weight || !output) return kBadArgument;
+    Call c;
+    if ((r = get_device_ctx(&c.ctx)) != kOk) return r;
+    c.st = reinterpret_cast<cudaStream_t>(stream);
+    c.cap = cap_for(c.ctx);
+    c.arena = nullptr;
+    // everything this call needs must fit into the fixed array: refuse before anything is launched
+    const size_t need = kNoAllocStatusBytes + x_scratch_bytes(input, s) + w_scratch_bytes(weight, s) +
+                        partial_bytes(c.cap, fwd_acc_arrays(FwdKind::Inf));
+    if (need > kNoAllocScratchBytes) return kWorkspace;
+    char* base = nullptr;
+    if ((r = noalloc_scratch_address(&base)) != kOk) return r;
+    Arena fixed{base + kNoAllocStatusBytes, kNoAllocScratchBytes - kNoAllocStatusBytes,
+                reinterpret_cast<int*>(base), nullptr};
+    c.arena = &fixed;
+    c.bump = Bump{fixed.base, 0, fixed.capacity};
+    View xv, wv;
+    if ((r = get_x_view(c, input, s, &xv)) != kOk) return r;
+    if ((r = get_w_view(c, weight, s, &wv)) != kOk) return r;
+    return run_forward(c, FwdKind::Inf, 0, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, INFINITY);
+}
+
+}  // extern "C"
+
