@@ -46,8 +46,8 @@ SLOTS = {"8": (4, 6, 6), "inf": (2, None, None), "general": (6, 6, 6)}
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--p", default="8")
     ap.add_argument("--batch", type=int, default=512)
@@ -92,7 +92,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", self.sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
             return
@@ -165,6 +165,7 @@ def run_ours(args, rank, world, local_rank):
     import l_inf_dist_net_v2_b200 as ldn
     from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
     from l_inf_dist_net_v2_b200._lib import lib
+    from l_inf_dist_net_v2_b200.parallel import allreduce_mean_
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -213,8 +214,7 @@ def run_ours(args, rank, world, local_rank):
         fwd()
         bwd()
         if world > 1:
-            dist.all_reduce(gw)
-            gw.div_(world)
+            allreduce_mean_([gw])
 
     # public-API step with host buffers
     w_param = w.clone().requires_grad_()
@@ -229,8 +229,7 @@ def run_ours(args, rank, world, local_rank):
         out = ldn.norm_dist(xin, w_param, p)
         out.backward(g_dev)
         if world > 1:
-            dist.all_reduce(w_param.grad)
-            w_param.grad.div_(world)
+            allreduce_mean_([w_param.grad])
         yh.copy_(out.detach(), non_blocking=True)
 
     def barrier():
@@ -365,6 +364,20 @@ def run_ours(args, rank, world, local_rank):
         for label in ("8", "inf", "37.5"):
             if label != args.p:
                 extra += kernel_rows(p_value(label), label, 10)
+        # p = inf certification kernels: value without indices, interval bounds at eps = 8/255
+        eps = 8.0 / 255.0
+        xl, xu = (x - eps).clamp(0, 1), (x + eps).clamp(0, 1)
+        yl, yu = torch.empty_like(y), torch.empty_like(y)
+        pl, pu = torch.empty_like(pos), torch.empty_like(pos)
+        for name, fn, slots in (
+                ("forward_nograd", lambda: C.inf_dist_forward_nograd(x, w, y, 1), 2),
+                ("bounds_nograd", lambda: C.bound_inf_dist_forward_nograd(xl, xu, w, yl, yu, 1), 4),
+                ("bounds_with_indices", lambda: C.bound_inf_dist_forward(xl, xu, w, yl, yu, pl, pu, 1), 4)):
+            t = statistics.median(event_ms_list(fn, 10, 3, flush))
+            ach = slots * pairs / (t * 1e-3) / 1e12
+            extra.append({"p": "inf", "kernel": name, "ms": round(t, 4), "gpair_per_s": round(pairs / (t * 1e-3) / 1e9, 1),
+                          "bound": "fp32", "slots_per_pair": slots, "tlaneop_per_s": round(ach, 2),
+                          "frac_of_ffma_probe": round(ach / ffma_peak, 3), "frac_of_nominal": round(ach / nominal_fp32, 3)})
         line["variants"] = extra
         fwd()
     C.check_status()

@@ -1,0 +1,66 @@
+"""World-size-2 CPU (gloo) test of the data-parallel plumbing: shard the batch, compute each rank's
+grad_weight with the CPU checker, all-reduce (mean), compare with the full-batch gradient."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from l_inf_dist_net_v2_b200.parallel import shard_batch, shard_bounds, allreduce_mean_, average_scalars
+    rng = np.random.default_rng(0)
+    B, CI, CO = 8, 24, 10
+    x = rng.random((B, CI, 1), dtype=np.float32)
+    w = rng.standard_normal((CO, CI)).astype(np.float32)
+    g = rng.standard_normal((B, CO, 1)).astype(np.float32)
+    lo, hi = shard_bounds(B, rank, world)
+    assert (lo, hi) == (rank * 4, rank * 4 + 4)
+    xs = shard_batch(torch.from_numpy(x), rank, world).numpy()
+    gs = g[lo:hi]
+    ys = oracle.norm_dist_forward(xs, w, 8.0)
+    _, gw_local = oracle.norm_dist_backward(gs, xs, w, ys, 8.0, want_gx=False)
+    gw = torch.from_numpy(gw_local.copy())
+    bias_grad = torch.full((CO,), float(rank + 1))
+    allreduce_mean_([gw, bias_grad], bucket_bytes=1 << 20)        # both in one bucket
+    gw2 = torch.from_numpy(gw_local.copy())
+    allreduce_mean_([gw2], bucket_bytes=16)                        # larger than a bucket: travels alone
+    y_full = oracle.norm_dist_forward(x, w, 8.0)
+    _, gw_full = oracle.norm_dist_backward(g, x, w, y_full, 8.0, want_gx=False)
+    ok = np.allclose(gw.numpy(), gw_full / world, rtol=1e-5, atol=1e-6)
+    ok = ok and np.allclose(gw2.numpy(), gw_full / world, rtol=1e-5, atol=1e-6)
+    ok = ok and torch.allclose(bias_grad, torch.full((CO,), 1.5))
+    m = average_scalars(float(rank), 2.0)
+    ok = ok and abs(m[0] - 0.5) < 1e-6 and abs(m[1] - 2.0) < 1e-6
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write("ok" if ok else "bad")
+    dist.destroy_process_group()
+
+
+def test_shard_and_allreduce_world2(tmp_path):
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"rank{r}.txt").read() == "ok"
+
+
+def test_shard_bounds_rejects_uneven_batches():
+    import pytest
+    from l_inf_dist_net_v2_b200.parallel import shard_bounds
+    with pytest.raises(ValueError):
+        shard_bounds(10, 0, 4)
+    assert shard_bounds(4096, 3, 8) == (1536, 2048)
