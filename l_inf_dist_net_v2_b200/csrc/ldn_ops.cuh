@@ -25,6 +25,41 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return r;
 }
 
+// 2^e on the FMA pipe: round e to the nearest integer n with the 1.5 * 2^23 trick, evaluate a minimax
+// polynomial of 2^f on f = e - n in [-0.5, 0.5] and add n to the exponent field.  Maximum relative
+// error 7.5e-5 (DEG 3) / 2.7e-6 (DEG 4).  e is clamped at -125 (the result is then ~2e-38 instead of 0);
+// e must stay below 126.
+template <int DEG>
+__device__ __forceinline__ float ex2_fma(float e) {
+    static_assert(DEG == 3 || DEG == 4, "supported polynomial degrees");
+    e = fmaxf(e, -125.0f);
+    const float magic = 12582912.0f;
+    const float z = e + magic;
+    const float f = e - (z - magic);
+    float pl;
+    if (DEG == 3) {
+        pl = fmaf(0.05517162010073662f, f, 0.2426111251115799f);
+        pl = fmaf(pl, f, 0.6932609677314758f);
+        pl = fmaf(pl, f, 0.9999280571937561f);
+    } else {
+        pl = fmaf(0.009570096619427204f, f, 0.05591785907745361f);
+        pl = fmaf(pl, f, 0.240247443318367f);
+        pl = fmaf(pl, f, 0.6931217908859253f);
+        pl = fmaf(pl, f, 0.9999992847442627f);
+    }
+    return __int_as_float(__float_as_int(pl) + (__float_as_int(z) << 23));
+}
+
+// The general-p kernels need two transcendentals per pair and are bound by the MUFU pipe (16 lanes per SM
+// against 128 FP32 lanes).  The logarithm stays on MUFU; the exponential goes to MUFU for one pair in
+// kMufuEvery and to the FMA-pipe polynomial for the others, which balances the two pipes.  `sel` is a
+// compile-time constant after unrolling (output slot + k).
+constexpr int kMufuEvery = 4;
+template <int DEG>
+__device__ __forceinline__ float ex2_mixed(float e, int sel) {
+    return (sel % kMufuEvery) == 0 ? ex2_approx(e) : ex2_fma<DEG>(e);
+}
+
 // |t|^IP by repeated multiplication, IP in 1..8
 template <int IP>
 __device__ __forceinline__ float abs_pow(float t) {
@@ -93,7 +128,7 @@ struct FwdPowInt : FwdLayout {
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     template <int KS>
-    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int,
+    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int, int,
                                    const TileParams&) {
 #pragma unroll
         for (int k = 0; k < KS; ++k) f[0] = acc_abs_pow<IP>(f[0], a[k] - b[k]);
@@ -111,10 +146,10 @@ struct FwdPowGen : FwdLayout {
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     template <int KS>
-    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int,
+    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int, int sel,
                                    const TileParams& P) {
 #pragma unroll
-        for (int k = 0; k < KS; ++k) f[0] += ex2_approx(P.p * lg2_approx(fabsf(a[k] - b[k])));
+        for (int k = 0; k < KS; ++k) f[0] += ex2_mixed<4>(P.p * lg2_approx(fabsf(a[k] - b[k])), sel + k);
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
@@ -130,10 +165,10 @@ struct FwdPowNorm : FwdLayout {
     static constexpr bool HAS_P = true;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     template <int KS>
-    __device__ static void update(float* f, int*, float cm, const float* a, const float*, const float* b, int,
+    __device__ static void update(float* f, int*, float cm, const float* a, const float*, const float* b, int, int sel,
                                    const TileParams& P) {
 #pragma unroll
-        for (int k = 0; k < KS; ++k) f[0] += ex2_approx(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm));
+        for (int k = 0; k < KS; ++k) f[0] += ex2_mixed<3>(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm), sel + k);
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
@@ -155,6 +190,7 @@ struct FwdPowNorm : FwdLayout {
 // ------------------------------------------------------------------------------------------------
 template <bool POS>
 struct FwdInf : FwdLayout {
+    static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
     static constexpr int NUM_A = 1, NF = 1, NI = POS ? 1 : 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int* n) {
@@ -163,7 +199,7 @@ struct FwdInf : FwdLayout {
     }
     template <int KS>
     __device__ static void update(float* f, int* n, float, const float* a, const float*, const float* b,
-                                   int chunk, const TileParams&) {
+                                   int chunk, int, const TileParams&) {
         float mm = fabsf(a[0] - b[0]);
 #pragma unroll
         for (int k = 1; k < KS; ++k) mm = fmaxf(mm, fabsf(a[k] - b[k]));
@@ -225,7 +261,7 @@ struct FwdBound : FwdLayout {
         f[1] = kEps;
     }
     template <int KS>
-    __device__ static void update(float* f, int*, float, const float* lo, const float* up, const float* w, int,
+    __device__ static void update(float* f, int*, float, const float* lo, const float* up, const float* w, int, int,
                                    const TileParams&) {
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
@@ -257,7 +293,7 @@ struct FwdBoundPos : FwdLayout {
     __device__ static float pick(float t1, float t2) { return UPPER ? fmaxf(t1, t2) : fminf(t1, t2); }
     template <int KS>
     __device__ static void update(float* f, int* n, float, const float* lo, const float* up, const float* w,
-                                   int chunk, const TileParams&) {
+                                   int chunk, int, const TileParams&) {
         float e = pick(w[0] - lo[0], up[0] - w[0]);
 #pragma unroll
         for (int k = 1; k < KS; ++k) {
@@ -333,7 +369,7 @@ struct BwdPowInt : BwdLayout<WEIGHT> {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     template <int KS>
-    __device__ static void update(float* f, int*, float pres, const float* c, const float*, const float* b, int,
+    __device__ static void update(float* f, int*, float pres, const float* c, const float*, const float* b, int, int,
                                    const TileParams&) {
 #pragma unroll
         for (int k = 0; k < KS; ++k) f[0] = fmaf(c[k], signed_pow<IQ>(L::diff(pres, b[k])), f[0]);
@@ -350,12 +386,12 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     template <int KS>
-    __device__ static void update(float* f, int*, float pres, const float* r, const float* gr, const float* b, int,
+    __device__ static void update(float* f, int*, float pres, const float* r, const float* gr, const float* b, int, int sel,
                                    const TileParams& P) {
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
             const float t = L::diff(pres, b[k]);
-            const float v = ex2_approx(P.q * lg2_approx(fabsf(t) * r[k]));
+            const float v = ex2_mixed<4>(P.q * lg2_approx(fabsf(t) * r[k]), sel + k);
             f[0] = fmaf(gr[k], copysignf(v, t), f[0]);
         }
     }

@@ -221,7 +221,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < kRegN; ++j)
                     Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], a0[i], NA == 2 ? a1[i] : a0[i], b[j],
-                                            chunk, P);
+                                            chunk, i + j, P);
         }
 
         if (kt == KT - 1 || it == it1 - 1) {
