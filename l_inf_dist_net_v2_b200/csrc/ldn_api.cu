@@ -204,8 +204,14 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     const int iq = int_power(p - 1.0f);
     const int ncoef = iq >= 0 ? 1 : 2;
     const size_t coef_floats = canonical_floats(s.COg, s.M, s.G);
+    // Both gradients wanted: one fused kernel evaluates every term once (grad_input accumulators plus
+    // per-row-tile column sums for grad_weight).  It needs tiles_m copies of grad_weight as scratch, so very
+    // tall problems (conv layouts with many rows) keep the two-kernel path; so does p = 1 (constant terms).
+    const long long tiles_m = (s.M + kTileM - 1) / kTileM;
+    const size_t side_floats = static_cast<size_t>(tiles_m) * s.CO * s.CIg;
+    const bool fused = gx && gw && iq != 0 && side_floats * sizeof(float) <= (size_t(1) << 30);
     size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + ncoef * pad256(coef_floats * sizeof(float)) +
-                  2 * partial_bytes(cap, 1);
+                  2 * partial_bytes(cap, 1) + (fused ? pad256(side_floats * sizeof(float)) : 0);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     View xv, wv;
@@ -220,6 +226,26 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(cv0.stride_row), c.st);
     if (r != kOk) return r;
 
+    if (fused) {
+        float* side = c.bump.take<float>(side_floats);
+        if (!side) return kWorkspace;
+        TileLaunch L;
+        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1)) != kOk) return r;
+        TileParams& P = L.params;
+        P.a_row_coord = cv0.row_coord;
+        P.b_row_coord = wv.row_coord;
+        P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(wv);
+        P.pres = as_operand(xv);
+        P.out = x_addr(s);
+        P.out_f0 = gx;
+        P.side_out = side;
+        P.p = p; P.q = p - 1.0f;
+        if ((r = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_b, wv, Layout::KMajor)) != kOk) return r;
+        if ((r = launch_bwd_fused(iq, L, c.st)) != kOk) return r;
+        return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m), c.st);
+    }
     if (gx) {
         // out (m = (b, hw), n = c), k = o
         TileLaunch L;

@@ -70,6 +70,7 @@ struct TileParams {
     int* out_i1;
     float p;                    // the exponent the op was called with
     float q;                    // op specific (p - 1 for backward)
+    float* side_out;            // fused backward: per-row-tile column sums [tile_m][g][k][n] (else null)
     float* partials;            // stream-K scratch: [grid][2][arrays][kTileElems]
     int* status;                // device status word (0 = ok)
     unsigned long long* trace;  // optional per-CTA trace: {sm id, start ns, end ns, iterations}; may be null

@@ -1,0 +1,18 @@
+#include "ldn_launch.cuh"
+#include "ldn_ops.cuh"
+
+namespace ldn {
+int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st) {
+    switch (iq) {
+        case 1: return launch_tile<BwdFusedInt<1>>(L, st);
+        case 2: return launch_tile<BwdFusedInt<2>>(L, st);
+        case 3: return launch_tile<BwdFusedInt<3>>(L, st);
+        case 4: return launch_tile<BwdFusedInt<4>>(L, st);
+        case 5: return launch_tile<BwdFusedInt<5>>(L, st);
+        case 6: return launch_tile<BwdFusedInt<6>>(L, st);
+        case 7: return launch_tile<BwdFusedInt<7>>(L, st);
+        case 8: return launch_tile<BwdFusedInt<8>>(L, st);
+        default: return launch_tile<BwdFusedGen>(L, st);
+    }
+}
+}  // namespace ldn

@@ -23,5 +23,6 @@ int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st); 
 int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper}
 int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st);                   // iq 0..8, or -1 for general p
 int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st);
+int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st);             // iq 1..8, or -1 for general p
 
 }  // namespace ldn

@@ -60,6 +60,40 @@ __device__ __forceinline__ float ex2_mixed(float e, int sel) {
     return (sel % kMufuEvery) == 0 ? ex2_approx(e) : ex2_fma<DEG>(e);
 }
 
+// Two-lane versions (packed FP32 instructions for the range reduction and the polynomial).  In the packed
+// kernels the exponential goes to MUFU for one output pair in EVERY.
+template <int DEG>
+__device__ __forceinline__ float2 ex2_fma2(float2 e) {
+    static_assert(DEG == 3 || DEG == 4, "supported polynomial degrees");
+    e.x = fmaxf(e.x, -125.0f);
+    e.y = fmaxf(e.y, -125.0f);
+    const float2 z = __fadd2_rn(e, make_float2(12582912.0f, 12582912.0f));
+    const float2 r = __fadd2_rn(z, make_float2(-12582912.0f, -12582912.0f));
+    const float2 f = __ffma2_rn(r, make_float2(-1.0f, -1.0f), e);
+    float2 pl;
+    if (DEG == 3) {
+        pl = __ffma2_rn(make_float2(0.05517162010073662f, 0.05517162010073662f), f,
+                        make_float2(0.2426111251115799f, 0.2426111251115799f));
+        pl = __ffma2_rn(pl, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+        pl = __ffma2_rn(pl, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+    } else {
+        pl = __ffma2_rn(make_float2(0.009570096619427204f, 0.009570096619427204f), f,
+                        make_float2(0.05591785907745361f, 0.05591785907745361f));
+        pl = __ffma2_rn(pl, f, make_float2(0.240247443318367f, 0.240247443318367f));
+        pl = __ffma2_rn(pl, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+        pl = __ffma2_rn(pl, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+    }
+    return make_float2(__int_as_float(__float_as_int(pl.x) + (__float_as_int(z.x) << 23)),
+                       __int_as_float(__float_as_int(pl.y) + (__float_as_int(z.y) << 23)));
+}
+template <int DEG, int EVERY>
+__device__ __forceinline__ float2 ex2_mixed2(float2 e, int sel) {
+    if ((sel % EVERY) == 0) return make_float2(ex2_approx(e.x), ex2_approx(e.y));
+    return ex2_fma2<DEG>(e);
+}
+constexpr int kMufuEveryFwd = 8;
+constexpr int kMufuEveryBwd = 4;
+
 // |t|^IP by repeated multiplication, IP in 1..8
 template <int IP>
 __device__ __forceinline__ float abs_pow(float t) {
@@ -111,10 +145,50 @@ __device__ __forceinline__ float signed_pow(float t) {
     return (t4 * t2) * u;
 }
 
+// ---- packed two-lane FP32 (sm_100 fma/mul/add .f32x2): one issue slot, two lane operations ---------
+__device__ __forceinline__ float2 pk(float x, float y) { return make_float2(x, y); }
+__device__ __forceinline__ float2 pk_abs(float2 t) { return make_float2(fabsf(t.x), fabsf(t.y)); }
+// x - y
+__device__ __forceinline__ float2 pk_sub(float2 x, float2 y) { return __ffma2_rn(y, make_float2(-1.0f, -1.0f), x); }
+
+// acc + |t|^IP on two lanes
+template <int IP>
+__device__ __forceinline__ float2 acc_abs_pow2(float2 acc, float2 t) {
+    if (IP == 1) return __fadd2_rn(acc, pk_abs(t));
+    if (IP == 2) return __ffma2_rn(t, t, acc);
+    const float2 t2 = __fmul2_rn(t, t);
+    if (IP == 3) return __ffma2_rn(t2, pk_abs(t), acc);
+    if (IP == 4) return __ffma2_rn(t2, t2, acc);
+    const float2 t4 = __fmul2_rn(t2, t2);
+    if (IP == 5) return __ffma2_rn(t4, pk_abs(t), acc);
+    if (IP == 6) return __ffma2_rn(t4, t2, acc);
+    if (IP == 7) return __ffma2_rn(t4, __fmul2_rn(t2, pk_abs(t)), acc);
+    return __ffma2_rn(t4, t4, acc);
+}
+
+// sgn(t) |t|^IQ on two lanes, IQ in 1..8 (sgn(t) = +1 for t >= 0; IQ = 0 is handled by the scalar path)
+template <int IQ>
+__device__ __forceinline__ float2 signed_pow2(float2 t) {
+    if (IQ == 1) return t;
+    if (IQ == 2) return __fmul2_rn(t, pk_abs(t));
+    const float2 t2 = __fmul2_rn(t, t);
+    if (IQ == 3) return __fmul2_rn(t2, t);
+    if (IQ == 4) return __fmul2_rn(t2, __fmul2_rn(t, pk_abs(t)));
+    const float2 t4 = __fmul2_rn(t2, t2);
+    if (IQ == 5) return __fmul2_rn(t4, t);
+    if (IQ == 6) return __fmul2_rn(t4, __fmul2_rn(t, pk_abs(t)));
+    if (IQ == 7) return __fmul2_rn(t4, __fmul2_rn(t2, t));
+    return __fmul2_rn(__fmul2_rn(t4, t2), __fmul2_rn(t, pk_abs(t)));
+}
+
 struct FwdLayout {
     static constexpr Layout LA = Layout::RowMajor;
     static constexpr Layout LB = Layout::RowMajor;
     static constexpr int KSTEP = 2;  // k values per rolled inner-loop step
+    static constexpr bool PACKED = false;
+    static constexpr bool PREFETCH = true;  // register double buffering of the operand slabs
+    static constexpr bool FUSED_W = false;
+    static constexpr int STAGES = kStages;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -124,9 +198,20 @@ struct FwdLayout {
 // sum of |t|^IP, then the p-th root with the underflow floor
 template <int IP>
 struct FwdPowInt : FwdLayout {
+    static constexpr int KSTEP = 4;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
+    static constexpr bool PACKED = true;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    template <int KS>
+    __device__ static void update_pair(float& s0, float& s1, float, float, const float* a, const float*,
+                                       const float* b0, const float* b1, int, const TileParams&) {
+        float2 acc = pk(s0, s1);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) acc = acc_abs_pow2<IP>(acc, pk(a[k] - b0[k], a[k] - b1[k]));
+        s0 = acc.x;
+        s1 = acc.y;
+    }
     template <int KS>
     __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int, int,
                                    const TileParams&) {
@@ -144,7 +229,22 @@ struct FwdPowInt : FwdLayout {
 struct FwdPowGen : FwdLayout {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
+    static constexpr bool PACKED = true;
+    static constexpr bool PREFETCH = false;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    template <int KS>
+    __device__ static void update_pair(float& s0, float& s1, float, float, const float* a, const float*,
+                                       const float* b0, const float* b1, int sel, const TileParams& P) {
+        float2 acc = make_float2(s0, s1);
+        const float2 pp = make_float2(P.p, P.p);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+            const float2 l = make_float2(lg2_approx(fabsf(a[k] - b0[k])), lg2_approx(fabsf(a[k] - b1[k])));
+            acc = __fadd2_rn(acc, ex2_mixed2<4, kMufuEveryFwd>(__fmul2_rn(pp, l), sel + k));
+        }
+        s0 = acc.x;
+        s1 = acc.y;
+    }
     template <int KS>
     __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int, int sel,
                                    const TileParams& P) {
@@ -163,7 +263,23 @@ struct FwdPowGen : FwdLayout {
 struct FwdPowNorm : FwdLayout {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = true;
+    static constexpr bool PACKED = true;
+    static constexpr bool PREFETCH = false;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    template <int KS>
+    __device__ static void update_pair(float& s0, float& s1, float cm0, float cm1, const float* a, const float*,
+                                       const float* b0, const float* b1, int sel, const TileParams& P) {
+        float2 acc = make_float2(s0, s1);
+        const float2 pp = make_float2(P.p, P.p);
+        const float2 cm = make_float2(cm0, cm1);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+            const float2 l = make_float2(lg2_approx(fabsf(a[k] - b0[k])), lg2_approx(fabsf(a[k] - b1[k])));
+            acc = __fadd2_rn(acc, ex2_mixed2<3, kMufuEveryFwd>(__ffma2_rn(pp, l, cm), sel + k));
+        }
+        s0 = acc.x;
+        s1 = acc.y;
+    }
     template <int KS>
     __device__ static void update(float* f, int*, float cm, const float* a, const float*, const float* b, int, int sel,
                                    const TileParams& P) {
@@ -191,6 +307,7 @@ struct FwdPowNorm : FwdLayout {
 template <bool POS>
 struct FwdInf : FwdLayout {
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
+    static constexpr bool PREFETCH = false;  // two 4-wide slabs would not fit the register file
     static constexpr int NUM_A = 1, NF = 1, NI = POS ? 1 : 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int* n) {
@@ -284,6 +401,7 @@ struct FwdBound : FwdLayout {
 
 template <bool UPPER>
 struct FwdBoundPos : FwdLayout {
+    static constexpr bool PREFETCH = false;
     static constexpr int NUM_A = 2, NF = 1, NI = 1;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int* n) {
@@ -353,6 +471,10 @@ struct BwdLayout {
     static constexpr Layout LA = WEIGHT ? Layout::KMajor : Layout::RowMajor;
     static constexpr Layout LB = Layout::KMajor;
     static constexpr int KSTEP = 2;
+    static constexpr bool PACKED = false;
+    static constexpr bool PREFETCH = false;  // the resident operand leaves no registers for it
+    static constexpr bool FUSED_W = false;
+    static constexpr int STAGES = kStages;
     static constexpr bool HAS_P = true;
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
         return P.pres.ptr[n + m * P.pres.stride_row + g * P.pres.stride_group];
@@ -367,7 +489,20 @@ template <int IQ, bool WEIGHT>
 struct BwdPowInt : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
+    static constexpr bool PACKED = IQ >= 1;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    template <int KS>
+    __device__ static void update_pair(float& s0, float& s1, float p0, float p1, const float* c, const float*,
+                                       const float* b0, const float* b1, int, const TileParams&) {
+        const float2 pr = pk(p0, p1);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+            const float2 bb = pk(b0[k], b1[k]);
+            const float2 sp = signed_pow2<(IQ >= 1 ? IQ : 1)>(WEIGHT ? pk_sub(bb, pr) : pk_sub(pr, bb));
+            s0 = fmaf(c[k], sp.x, s0);
+            s1 = fmaf(c[k], sp.y, s1);
+        }
+    }
     template <int KS>
     __device__ static void update(float* f, int*, float pres, const float* c, const float*, const float* b, int, int,
                                    const TileParams&) {
@@ -384,7 +519,23 @@ template <bool WEIGHT>
 struct BwdPowGen : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
+    static constexpr bool PACKED = true;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    template <int KS>
+    __device__ static void update_pair(float& s0, float& s1, float p0, float p1, const float* r, const float* gr,
+                                       const float* b0, const float* b1, int sel, const TileParams& P) {
+        const float2 pr = make_float2(p0, p1);
+        const float2 qq = make_float2(P.q, P.q);
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+            const float2 bb = make_float2(b0[k], b1[k]);
+            const float2 t = WEIGHT ? pk_sub(bb, pr) : pk_sub(pr, bb);
+            const float2 l = make_float2(lg2_approx(fabsf(t.x) * r[k]), lg2_approx(fabsf(t.y) * r[k]));
+            const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__fmul2_rn(qq, l), sel + k);
+            s0 = fmaf(gr[k], copysignf(v.x, t.x), s0);
+            s1 = fmaf(gr[k], copysignf(v.y, t.y), s1);
+        }
+    }
     template <int KS>
     __device__ static void update(float* f, int*, float pres, const float* r, const float* gr, const float* b, int, int sel,
                                    const TileParams& P) {
@@ -394,6 +545,51 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
             const float v = ex2_mixed<4>(P.q * lg2_approx(fabsf(t) * r[k]), sel + k);
             f[0] = fmaf(gr[k], copysignf(v, t), f[0]);
         }
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        L::store(f[0], m, n, g, P);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// Fused backward (grad_input and grad_weight from one evaluation of every term).  The problem is the
+// grad_x one (out (m = (b, hw), n = c), k = o, resident x); in addition the engine sums every term over
+// the 128 rows of the CTA's tile and writes those column sums per row tile, [tile_m][g][o][c]; a small
+// kernel adds the row tiles and negates (side_reduce_kernel).  Every (tile_m, o, c) is produced by
+// exactly one CTA, so the result is deterministic.
+// ------------------------------------------------------------------------------------------------
+template <int IQ>
+struct BwdFusedInt : BwdLayout<false> {
+    using L = BwdLayout<false>;
+    static constexpr int NUM_A = 1, NF = 1, NI = 0;
+    static constexpr bool PACKED = true;
+    static constexpr bool FUSED_W = true;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static float2 term_pair(float p0, float p1, float c, float, float b0, float b1, int,
+                                       const TileParams&) {
+        const float2 sp = signed_pow2<IQ>(pk_sub(make_float2(p0, p1), make_float2(b0, b1)));
+        return __fmul2_rn(sp, make_float2(c, c));
+    }
+    __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
+    __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
+        L::store(f[0], m, n, g, P);
+    }
+};
+
+struct BwdFusedGen : BwdLayout<false> {
+    using L = BwdLayout<false>;
+    static constexpr int NUM_A = 2, NF = 1, NI = 0;
+    static constexpr bool PACKED = true;
+    static constexpr bool FUSED_W = true;
+    static constexpr int STAGES = 3;
+    __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    __device__ static float2 term_pair(float p0, float p1, float r, float gr, float b0, float b1, int sel,
+                                       const TileParams& P) {
+        const float2 t = pk_sub(make_float2(p0, p1), make_float2(b0, b1));
+        const float2 l = make_float2(lg2_approx(fabsf(t.x) * r), lg2_approx(fabsf(t.y) * r));
+        const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__fmul2_rn(make_float2(P.q, P.q), l), sel);
+        return make_float2(gr * copysignf(v.x, t.x), gr * copysignf(v.y, t.y));
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {

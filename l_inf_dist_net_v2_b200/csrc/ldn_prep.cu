@@ -90,6 +90,14 @@ __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __res
     }
 }
 
+__global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        float s = 0.0f;
+        for (int t = 0; t < tiles; ++t) s += part[t * count + i];
+        gw[i] = -s;
+    }
+}
+
 // One thread per output element, in output-layout order (coalesced reads of go / pos).
 __global__ void inf_scatter_kernel(const float* __restrict__ go, const int* __restrict__ pos, float* gx, float* gw,
                                    Shape s) {
@@ -164,6 +172,11 @@ int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
                     cudaStream_t st) {
     coef_gen_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, rinv, gcp, s, pitch);
+    LDN_LAUNCH_RET();
+}
+
+int launch_side_reduce(const float* part, float* gw, long long count, int tiles, cudaStream_t st) {
+    side_reduce_kernel<<<blocks_for(count), kBlock, 0, st>>>(part, gw, count, tiles);
     LDN_LAUNCH_RET();
 }
 

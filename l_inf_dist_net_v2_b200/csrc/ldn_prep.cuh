@@ -23,6 +23,9 @@ int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
                     cudaStream_t st);
 
+// grad_weight of the fused backward: gw[i] = -sum_t part[t * count + i], t < tiles
+int launch_side_reduce(const float* part, float* gw, long long count, int tiles, cudaStream_t st);
+
 // p = inf backward: gx[b, idx] += v, gw[o, idx] -= v with v = pos >= 0 ? go : -go.  gx / gw may be null.
 int launch_inf_scatter(const float* go, const int* pos, float* gx, float* gw, const Shape& s, cudaStream_t st);
 // interval-bound backward (see ldn_bound_inf_dist_backward_input_weight).  gw may be null.

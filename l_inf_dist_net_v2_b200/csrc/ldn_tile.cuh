@@ -23,7 +23,7 @@ namespace ldn {
 
 enum class Layout { RowMajor, KMajor };
 
-constexpr int kStages = 4;
+constexpr int kStages = 4;  // default depth of the operand ring (Op::STAGES)
 
 template <Layout L>
 __device__ __forceinline__ int own_index(int t, int r) {
@@ -90,10 +90,25 @@ __host__ __device__ __forceinline__ long long range_begin(long long total, int g
     return (total * c) / grid;
 }
 
+// Position of a thread in the 16 x 16 thread grid.  Default: a warp holds 2 rows x 16 columns of threads.
+// Fused-backward ops put 16 rows x 2 columns into a warp, so that the sum over the tile's rows is a
+// shuffle reduction inside the warp.
+template <class Op>
+__device__ __forceinline__ int thread_row(int tid) {
+    return Op::FUSED_W ? (tid & 15) : (tid >> 4);
+}
+template <class Op>
+__device__ __forceinline__ int thread_col(int tid) {
+    return Op::FUSED_W ? (((tid >> 4) & 1) + 2 * (tid >> 5)) : (tid & 15);
+}
+
+constexpr int kSideBufferBytes = kTileK * kTileN * 4;  // column sums of one stage (fused backward)
+
 template <class Op>
 struct TileSmem {
     static constexpr int kStage = (Op::NUM_A + 1) * kOperandTileBytes;
-    static constexpr int kTotal = kStages * kStage + 1024 /*alignment slack*/ + 64 /*barriers*/;
+    static constexpr int kSide = Op::FUSED_W ? 2 * kSideBufferBytes : 0;
+    static constexpr int kTotal = Op::STAGES * kStage + kSide + 1024 /*alignment slack*/ + 64 /*barriers*/;
 };
 
 template <class Op>
@@ -105,14 +120,16 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     constexpr int NI = Op::NI;
     constexpr int NIA = NI > 0 ? NI : 1;
     constexpr int STAGE = TileSmem<Op>::kStage;
+    constexpr int STAGES = Op::STAGES;
 
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * STAGE);
+    float* side = reinterpret_cast<float*>(smem + STAGES * STAGE);  // two column-sum buffers (fused backward)
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE + TileSmem<Op>::kSide);
 
     const int tid = threadIdx.x;
-    const int tn = tid & 15;
-    const int tm = tid >> 4;
+    const int tn = thread_col<Op>(tid);
+    const int tm = thread_row<Op>(tid);
     const int grid = gridDim.x;
     const long long it0 = range_begin(P.total_iters, grid, blockIdx.x);
     const long long it1 = range_begin(P.total_iters, grid, blockIdx.x + 1);
@@ -126,18 +143,18 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         if (NA == 2) tma_prefetch_desc(&map_a1);
         tma_prefetch_desc(&map_b);
 #pragma unroll
-        for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
         mbar_fence_init();
     }
     __syncthreads();
 
-    // producer side (thread 0): fill stage `ls % kStages` with the operands of iteration `it`
+    // producer side (thread 0): fill stage `ls % STAGES` with the operands of iteration `it`
     auto issue = [&](long long it, int ls) {
         const long long tile = it / KT;
         const int kt = static_cast<int>(it - tile * KT);
         const TileCoord tc = tile_coord(P, tile);
-        char* st = smem + (ls % kStages) * STAGE;
-        uint64_t* bar = &full[ls % kStages];
+        char* st = smem + (ls % STAGES) * STAGE;
+        uint64_t* bar = &full[ls % STAGES];
         mbar_expect_tx(bar, STAGE);
         const int k0 = kt * kTileK;
         {
@@ -158,9 +175,41 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     };
 
     if (tid == 0) {
-        for (int s = 0; s < kStages - 1; ++s)
+        for (int s = 0; s < STAGES - 1; ++s)
             if (it0 + s < it1) issue(it0 + s, s);
     }
+
+    // fused backward: write the column sums of a finished stage (rows = its 32 k values) to
+    // side_out[tile_m][g][k][n]
+    auto flush_side = [&](long long it_done, int buf) {
+        const long long tile_d = it_done / KT;
+        const int kt_d = static_cast<int>(it_done - tile_d * KT);
+        const TileCoord cd = tile_coord(P, tile_d);
+        float* src = side + buf * (kTileK * kTileN);
+        float* dst_tile = P.side_out + (static_cast<size_t>(cd.m0 / kTileM) * P.G + cd.g) * (size_t)P.K * P.N;
+        const bool vec = (P.N & 3) == 0;
+#pragma unroll
+        for (int q = 0; q < (kTileK * kTileN / 4) / kThreads; ++q) {
+            const int idx4 = tid + kThreads * q;
+            const int r = idx4 >> 5;
+            const int c4 = (idx4 & 31) * 4;
+            float4* sp = reinterpret_cast<float4*>(src + r * kTileN + c4);
+            const float4 v = *sp;
+            const int o = kt_d * kTileK + r;
+            const int n = cd.n0 + c4;
+            if (o < P.K && n < P.N) {
+                float* dst = dst_tile + static_cast<size_t>(o) * P.N + n;
+                if (vec) {
+                    *reinterpret_cast<float4*>(dst) = v;
+                } else {
+                    dst[0] = v.x;
+                    if (n + 1 < P.N) dst[1] = v.y;
+                    if (n + 2 < P.N) dst[2] = v.z;
+                    if (n + 3 < P.N) dst[3] = v.w;
+                }
+            }
+        }
+    };
 
     float accf[kRegM][kRegN][NF];
     int acci[kRegM][kRegN][NIA];
@@ -191,14 +240,17 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 }
         }
 
-        if (!mbar_wait_bounded(&full[ls % kStages], (ls / kStages) & 1)) {
+        if (!mbar_wait_bounded(&full[ls % STAGES], (ls / STAGES) & 1)) {
             atomicExch(P.status, static_cast<int>(kDeviceTimeout));
             return;
         }
         __syncthreads();  // every warp is done with the stage that is refilled next
-        if (tid == 0 && it + (kStages - 1) < it1) issue(it + (kStages - 1), ls + (kStages - 1));
+        if (tid == 0 && it + (STAGES - 1) < it1) issue(it + (STAGES - 1), ls + (STAGES - 1));
+        if constexpr (Op::FUSED_W) {
+            if (ls > 0) flush_side(it - 1, (ls - 1) & 1);
+        }
 
-        const char* sa0 = smem + (ls % kStages) * STAGE;
+        const char* sa0 = smem + (ls % STAGES) * STAGE;
         const char* sa1 = sa0 + (NA == 2 ? kOperandTileBytes : 0);
         const char* sb = sa0 + NA * kOperandTileBytes;
         // The k-groups of a stage are walked in a rolled loop so that the loop body (64 outputs x KS k x
@@ -207,21 +259,106 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         // makes the narrower shared-memory reads of a RowMajor B tile bank-conflict free.  The order in
         // which a thread visits k does not matter to any op (sums, exact min / max, 4-channel groups).
         constexpr int KS = Op::KSTEP;
-        const int perm = (KS < 4) ? (tn >> 3) : 0;
-#pragma unroll 1
-        for (int ks = 0; ks < kTileK / KS; ++ks) {
-            const int ps = ks ^ perm;
+        constexpr int NSTEP = kTileK / KS;
+        // (fused-backward ops reduce across the lanes of a warp per k, so all lanes must visit k in the same
+        // order: no swap there, at the price of a 2-way conflict on their narrow RowMajor reads)
+        const int perm = (KS < 4 && !Op::FUSED_W) ? (tn >> 3) : 0;
+        struct Slab {
             float a0[8][KS], a1[8][KS], b[8][KS];
-            fetch_slab<Op::LA, KS>(sa0, tm, ps, a0);
-            if (NA == 2) fetch_slab<Op::LA, KS>(sa1, tm, ps, a1);
-            fetch_slab<Op::LB, KS>(sb, tn, ps, b);
+        };
+        auto load = [&](Slab& sl, int ks) {
+            const int ps = ks ^ perm;
+            fetch_slab<Op::LA, KS>(sa0, tm, ps, sl.a0);
+            if (NA == 2) fetch_slab<Op::LA, KS>(sa1, tm, ps, sl.a1);
+            fetch_slab<Op::LB, KS>(sb, tn, ps, sl.b);
+        };
+        auto compute = [&](const Slab& sl, int ks) {
+            const int ps = ks ^ perm;
             const int chunk = kt * (kTileK / 4) + ((ps * KS) >> 2);
+            if constexpr (Op::FUSED_W) {
+                // Fused backward: every term feeds the thread's own accumulator (grad_input, reduced over k)
+                // and a column sum over the CTA's 128 rows (grad_weight of this row tile): summed over the
+                // thread's 8 rows in registers and over the warp's 16 row groups by shuffles; the finished
+                // column sums go to the stage's buffer with plain stores (every column has one owner).
+                float* buf = side + (ls & 1) * (kTileK * kTileN);
 #pragma unroll
-            for (int i = 0; i < kRegM; ++i)
+                for (int k = 0; k < KS; ++k) {
+                    float2 col[kRegN / 2];
 #pragma unroll
-                for (int j = 0; j < kRegN; ++j)
-                    Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], a0[i], NA == 2 ? a1[i] : a0[i], b[j],
-                                            chunk, i + j, P);
+                    for (int jp = 0; jp < kRegN / 2; ++jp) col[jp] = make_float2(0.0f, 0.0f);
+#pragma unroll
+                    for (int i = 0; i < kRegM; ++i)
+#pragma unroll
+                        for (int jp = 0; jp < kRegN / 2; ++jp) {
+                            const float2 term = Op::term_pair(pres[i][2 * jp], pres[i][2 * jp + 1], sl.a0[i][k],
+                                                              NA == 2 ? sl.a1[i][k] : 0.0f, sl.b[2 * jp][k],
+                                                              sl.b[2 * jp + 1][k], i + jp + k, P);
+                            const float2 acc =
+                                __fadd2_rn(make_float2(accf[i][2 * jp][0], accf[i][2 * jp + 1][0]), term);
+                            accf[i][2 * jp][0] = acc.x;
+                            accf[i][2 * jp + 1][0] = acc.y;
+                            col[jp] = __fadd2_rn(col[jp], term);
+                        }
+                    // Sum over the 16 row groups of the warp (lane bits 0..3) with a halving butterfly:
+                    // each exchange step passes on half of the values a lane still holds, so 8 values need
+                    // 4 + 2 + 1 shuffles plus one full step, and every lane ends with one finished column.
+                    const bool b3 = (tid & 8) != 0, b2 = (tid & 4) != 0, b1 = (tid & 2) != 0;
+                    float v4[4], v2[2], v1;
+                    {
+                        const float c0 = col[0].x, c1 = col[0].y, c2 = col[1].x, c3 = col[1].y;
+                        const float c4 = col[2].x, c5 = col[2].y, c6 = col[3].x, c7 = col[3].y;
+                        v4[0] = (b3 ? c4 : c0) + __shfl_xor_sync(0xffffffffu, b3 ? c0 : c4, 8);
+                        v4[1] = (b3 ? c5 : c1) + __shfl_xor_sync(0xffffffffu, b3 ? c1 : c5, 8);
+                        v4[2] = (b3 ? c6 : c2) + __shfl_xor_sync(0xffffffffu, b3 ? c2 : c6, 8);
+                        v4[3] = (b3 ? c7 : c3) + __shfl_xor_sync(0xffffffffu, b3 ? c3 : c7, 8);
+                    }
+                    v2[0] = (b2 ? v4[2] : v4[0]) + __shfl_xor_sync(0xffffffffu, b2 ? v4[0] : v4[2], 4);
+                    v2[1] = (b2 ? v4[3] : v4[1]) + __shfl_xor_sync(0xffffffffu, b2 ? v4[1] : v4[3], 4);
+                    v1 = (b1 ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, b1 ? v2[0] : v2[1], 2);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                    if ((tid & 1) == 0) {
+                        const int j = (b3 ? 4 : 0) + (b2 ? 2 : 0) + (b1 ? 1 : 0);
+                        buf[(ps * KS + k) * kTileN + own_index<Layout::KMajor>(tn, j)] = v1;
+                    }
+                }
+            } else if constexpr (Op::PACKED) {
+                // two neighbouring outputs (j, j + 1) at a time, so that the op can use the packed
+                // two-lane FP32 instructions (fma.rn.f32x2 ...): half the issue slots per lane operation
+#pragma unroll
+                for (int i = 0; i < kRegM; ++i)
+#pragma unroll
+                    for (int j = 0; j < kRegN; j += 2)
+                        Op::template update_pair<KS>(accf[i][j][0], accf[i][j + 1][0], pres[i][j], pres[i][j + 1],
+                                                     sl.a0[i], NA == 2 ? sl.a1[i] : sl.a0[i], sl.b[j], sl.b[j + 1],
+                                                     i + (j >> 1), P);
+            } else {
+#pragma unroll
+                for (int i = 0; i < kRegM; ++i)
+#pragma unroll
+                    for (int j = 0; j < kRegN; ++j)
+                        Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], sl.a0[i],
+                                                NA == 2 ? sl.a1[i] : sl.a0[i], sl.b[j], chunk, i + j, P);
+            }
+        };
+        if constexpr (Op::PREFETCH) {
+            // register double buffering: the operands of the next k-group are read from shared memory
+            // while the current group is computed (the loop is rolled, the compiler cannot do this itself)
+            Slab s0, s1;
+            load(s0, 0);
+#pragma unroll 1
+            for (int ks = 0; ks < NSTEP; ks += 2) {
+                load(s1, ks + 1);
+                compute(s0, ks);
+                if (ks + 2 < NSTEP) load(s0, ks + 2);
+                compute(s1, ks + 1);
+            }
+        } else {
+#pragma unroll 1
+            for (int ks = 0; ks < NSTEP; ++ks) {
+                Slab sl;
+                load(sl, ks);
+                compute(sl, ks);
+            }
         }
 
         if (kt == KT - 1 || it == it1 - 1) {
@@ -252,6 +389,10 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
             }
         }
     }
+    if constexpr (Op::FUSED_W) {
+        __syncthreads();
+        flush_side(it1 - 1, static_cast<int>((it1 - 1 - it0) & 1));
+    }
     if (P.trace && tid == 0) {
         unsigned long long* tr = P.trace + 4ull * blockIdx.x;
         tr[0] = sm_id();
@@ -278,8 +419,8 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
     if (range_begin(P.total_iters, main_grid, c + 1) >= t1) return;  // owned whole by one CTA
 
     const int tid = threadIdx.x;
-    const int tn = tid & 15;
-    const int tm = tid >> 4;
+    const int tn = thread_col<Op>(tid);
+    const int tm = thread_row<Op>(tid);
     const TileCoord tc = tile_coord(P, tile);
     float accf[kRegM][kRegN][NF];
     int acci[kRegM][kRegN][NIA];

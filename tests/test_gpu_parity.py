@@ -92,7 +92,8 @@ def test_golden_finite_p(C, golden, max_ctas):
             assert rel_to_max(gw.cpu().numpy(), golden[f"{key}/p{p}/gw"]) < tol, (key, p)
             gx2 = torch.full(x.shape, float("nan"), device="cuda")
             C.norm_dist_backward_input(dev(g), dev(x), dev(w), y, gx2, G, p)
-            assert torch.equal(gx, gx2), (key, p)
+            # grad_input alone and the fused grad_input + grad_weight kernel round differently
+            assert rel_to_max(gx2.cpu().numpy(), golden[f"{key}/p{p}/gx"]) < tol, (key, p)
     lib.ldn_set_max_ctas(0)
     C.check_status()
 
@@ -193,7 +194,10 @@ def test_finite_p_against_checker(C, shape, p):
         assert rel_to_max(gx.cpu().numpy(), ogx) < tol, (shape, p, max_ctas)
         assert rel_to_max(gw.cpu().numpy(), ogw) < tol, (shape, p, max_ctas)
         _, gw_only = run_backward(C, g, x, w, y, p, G, want_gx=False)
-        assert torch.equal(gw, gw_only)
+        assert rel_to_max(gw_only.cpu().numpy(), ogw) < tol, (shape, p, max_ctas)
+        gx_only = torch.full(x.shape, float("nan"), device="cuda")
+        C.norm_dist_backward_input(dev(g), dev(x), dev(w), y, gx_only, G, p)
+        assert rel_to_max(gx_only.cpu().numpy(), ogx) < tol, (shape, p, max_ctas)
     lib.ldn_set_max_ctas(0)
     C.check_status()
 
