@@ -295,7 +295,9 @@ int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* p
     View xv, wv;
     if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
     if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
-    return run_forward(c, kind, 0, xv, nullptr, wv, s, y, nullptr, pos, nullptr, nullptr, INFINITY);
+    r = run_forward(c, kind, 0, xv, nullptr, wv, s, y, nullptr, pos, nullptr, nullptr, INFINITY);
+    if (r != kOk || !pos) return r;
+    return launch_rescan(0, as_operand(xv), as_operand(xv), as_operand(wv), y, pos, s, c.st);
 }
 
 int bound_forward(const float* xl, const float* xu, const float* w, const Shape& s, float* yl, float* yu, int* pl,
@@ -305,7 +307,7 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
     const size_t xfloats = canonical_floats(s.CIg, s.M, s.G);
-    size_t need = 2 * pad256(xfloats * sizeof(float)) + w_scratch_bytes(w, s) + 2 * partial_bytes(cap_for(ctx), 2);
+    size_t need = 2 * pad256(xfloats * sizeof(float)) + w_scratch_bytes(w, s) + 2 * partial_bytes(cap_for(ctx), 3);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     float* lc = c.bump.take<float>(xfloats);
@@ -319,7 +321,10 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
     if (!pl) return run_forward(c, FwdKind::Bound, 0, lv, &uv, wv, s, yl, yu, nullptr, nullptr, nullptr, INFINITY);
     r = run_forward(c, FwdKind::BoundPosLower, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
     if (r != kOk) return r;
-    return run_forward(c, FwdKind::BoundPosUpper, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
+    if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st)) != kOk) return r;
+    r = run_forward(c, FwdKind::BoundPosUpper, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
+    if (r != kOk) return r;
+    return launch_rescan(2, as_operand(lv), as_operand(uv), as_operand(wv), yu, pu, s, c.st);
 }
 
 }  // namespace

@@ -10,10 +10,10 @@ enum class FwdKind { PowInt, PowGen, PowNorm, Inf, InfPos, Bound, BoundPosLower,
 // number of accumulator arrays (float + int) an op keeps per output: sizes the stream-K scratch
 inline int fwd_acc_arrays(FwdKind k) {
     switch (k) {
-        case FwdKind::InfPos: return 2;
+        case FwdKind::InfPos: return 3;
         case FwdKind::Bound: return 2;
-        case FwdKind::BoundPosLower: return 2;
-        case FwdKind::BoundPosUpper: return 2;
+        case FwdKind::BoundPosLower: return 3;
+        case FwdKind::BoundPosUpper: return 3;
         default: return 1;
     }
 }

@@ -188,6 +188,7 @@ struct FwdLayout {
     static constexpr bool PACKED = false;
     static constexpr bool PREFETCH = true;  // register double buffering of the operand slabs
     static constexpr bool FUSED_W = false;
+    static constexpr bool STAGE_HOOK = false;  // op has a stage_end(f, n, stage) step after every 32-wide stage
     static constexpr int STAGES = kStages;
 };
 
@@ -300,33 +301,44 @@ struct FwdPowNorm : FwdLayout {
 
 // ------------------------------------------------------------------------------------------------
 // p = inf, forward.  The running maximum is exact whatever the evaluation order.  With POS the kernel
-// also records in which group of 4 consecutive channels the maximum first strictly increased to its
-// final value; finalize rescans those 4 channels for the first one equal to the maximum, which is the
-// index a strictly-greater scan in ascending channel order ends with.
+// also records in which 32-channel stage the maximum first strictly increased to its final value (one
+// compare per output per stage, the inner loop stays the plain maximum) and stores that stage id in the
+// index array; rescan_kernel (ldn_prep.cu, one thread per output) then finds the
+// first channel equal to the maximum, which is the index a strictly-greater scan in ascending channel
+// order ends with.
 // ------------------------------------------------------------------------------------------------
 template <bool POS>
 struct FwdInf : FwdLayout {
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
     static constexpr bool PREFETCH = false;  // two 4-wide slabs would not fit the register file
-    static constexpr int NUM_A = 1, NF = 1, NI = POS ? 1 : 0;
+    // POS: f[0] = running maximum, f[1] = maximum inside the current 32-channel stage, n[0] = stage in which
+    // the running maximum last strictly increased (-1: never)
+    static constexpr int NUM_A = 1, NF = POS ? 2 : 1, NI = POS ? 1 : 0;
     static constexpr bool HAS_P = false;
+    static constexpr bool STAGE_HOOK = POS;
     __device__ static void init(float* f, int* n) {
         f[0] = kEps;
-        if (POS) n[0] = -1;
+        if (POS) {
+            f[1] = 0.0f;
+            n[0] = -1;
+        }
     }
     template <int KS>
-    __device__ static void update(float* f, int* n, float, const float* a, const float*, const float* b,
-                                   int chunk, int, const TileParams&) {
-        float mm = fabsf(a[0] - b[0]);
+    __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int, int,
+                                  const TileParams&) {
+        float& m = f[POS ? 1 : 0];
 #pragma unroll
-        for (int k = 1; k < KS; ++k) mm = fmaxf(mm, fabsf(a[k] - b[k]));
+        for (int k = 0; k < KS; ++k) m = fmaxf(m, fabsf(a[k] - b[k]));
+    }
+    // end of a 32-channel stage: stages are visited in ascending order, so a strict comparison keeps the
+    // first stage that reaches the final maximum
+    __device__ static void stage_end(float* f, int* n, int stage) {
         if (POS) {
-            if (mm > f[0]) {
-                f[0] = mm;
-                n[0] = chunk;
+            if (f[1] > f[0]) {
+                f[0] = f[1];
+                n[0] = stage;
             }
-        } else {
-            f[0] = fmaxf(f[0], mm);
+            f[1] = 0.0f;
         }
     }
     __device__ static void combine(float* f, int* n, const float* pf, const int* pn) {
@@ -343,23 +355,7 @@ struct FwdInf : FwdLayout {
     __device__ static void finalize(const float* f, const int* nn, float, int m, int n, int g, const TileParams& P) {
         const long long off = out_offset(P.out, m, n, g);
         P.out_f0[off] = f[0];
-        if (POS) {
-            int pos = 0;
-            if (nn[0] >= 0) {
-                const float* ar = P.a0.ptr + m * P.a0.stride_row + g * P.a0.stride_group;
-                const float* br = P.b.ptr + n * P.b.stride_row + g * P.b.stride_group;
-                for (int kk = 0; kk < 4; ++kk) {
-                    const int k = nn[0] * 4 + kk;
-                    if (k >= P.K) break;
-                    const float t = ar[k] - br[k];
-                    if (fabsf(t) == f[0]) {
-                        pos = k | (t >= 0.0f ? 0 : kSignBit);
-                        break;
-                    }
-                }
-            }
-            P.out_i0[off] = pos;
-        }
+        if (POS) P.out_i0[off] = nn[0];  // stage id (or -1); turned into the index by rescan_kernel
     }
 };
 
@@ -402,26 +398,32 @@ struct FwdBound : FwdLayout {
 template <bool UPPER>
 struct FwdBoundPos : FwdLayout {
     static constexpr bool PREFETCH = false;
-    static constexpr int NUM_A = 2, NF = 1, NI = 1;
+    // f[0] = running extremum, f[1] = extremum inside the current stage, n[0] = stage of the last strict
+    // improvement (-1: never), as in FwdInf<true>
+    static constexpr int NUM_A = 2, NF = 2, NI = 1;
     static constexpr bool HAS_P = false;
+    static constexpr bool STAGE_HOOK = true;
     __device__ static void init(float* f, int* n) {
         f[0] = UPPER ? kEps : -kEps;
+        f[1] = UPPER ? -FLT_MAX : FLT_MAX;
         n[0] = -1;
     }
     __device__ static float pick(float t1, float t2) { return UPPER ? fmaxf(t1, t2) : fminf(t1, t2); }
     template <int KS>
-    __device__ static void update(float* f, int* n, float, const float* lo, const float* up, const float* w,
-                                   int chunk, int, const TileParams&) {
-        float e = pick(w[0] - lo[0], up[0] - w[0]);
+    __device__ static void update(float* f, int*, float, const float* lo, const float* up, const float* w, int, int,
+                                  const TileParams&) {
 #pragma unroll
-        for (int k = 1; k < KS; ++k) {
+        for (int k = 0; k < KS; ++k) {
             const float t1 = w[k] - lo[k], t2 = up[k] - w[k];
-            e = UPPER ? fmaxf(fmaxf(e, t1), t2) : fminf(fminf(e, t1), t2);
+            f[1] = UPPER ? fmaxf(fmaxf(f[1], t1), t2) : fminf(fminf(f[1], t1), t2);
         }
-        if (UPPER ? (e > f[0]) : (e < f[0])) {
-            f[0] = e;
-            n[0] = chunk;
+    }
+    __device__ static void stage_end(float* f, int* n, int stage) {
+        if (UPPER ? (f[1] > f[0]) : (f[1] < f[0])) {
+            f[0] = f[1];
+            n[0] = stage;
         }
+        f[1] = UPPER ? -FLT_MAX : FLT_MAX;
     }
     __device__ static void combine(float* f, int* n, const float* pf, const int* pn) {
         if (UPPER ? (pf[0] > f[0]) : (pf[0] < f[0])) {
@@ -432,21 +434,7 @@ struct FwdBoundPos : FwdLayout {
     __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
     __device__ static void finalize(const float* f, const int* nn, float, int m, int n, int g, const TileParams& P) {
         const long long off = out_offset(P.out, m, n, g);
-        int pos = UPPER ? 0 : kNoGrad;
-        if (nn[0] >= 0) {
-            const float* lr = P.a0.ptr + m * P.a0.stride_row + g * P.a0.stride_group;
-            const float* ur = P.a1.ptr + m * P.a1.stride_row + g * P.a1.stride_group;
-            const float* wr = P.b.ptr + n * P.b.stride_row + g * P.b.stride_group;
-            for (int kk = 0; kk < 4; ++kk) {
-                const int k = nn[0] * 4 + kk;
-                if (k >= P.K) break;
-                const float t1 = wr[k] - lr[k], t2 = ur[k] - wr[k];
-                if (pick(t1, t2) == f[0]) {
-                    pos = k | (t1 <= t2 ? 0 : kSignBit);
-                    break;
-                }
-            }
-        }
+        const int pos = nn[0];  // stage id (or -1); turned into the index by rescan_kernel
         if (UPPER) {
             P.out_f1[off] = f[0];
             P.out_i1[off] = pos;
@@ -474,6 +462,7 @@ struct BwdLayout {
     static constexpr bool PACKED = false;
     static constexpr bool PREFETCH = false;  // the resident operand leaves no registers for it
     static constexpr bool FUSED_W = false;
+    static constexpr bool STAGE_HOOK = false;
     static constexpr int STAGES = kStages;
     static constexpr bool HAS_P = true;
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {

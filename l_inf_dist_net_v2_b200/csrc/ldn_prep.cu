@@ -90,6 +90,63 @@ __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __res
     }
 }
 
+// One thread per output element: 8 independent 16-byte loads per operand cover the recorded stage (operand
+// views are 16-byte aligned with row pitches that are multiples of 4 floats), then an in-register
+// descending scan keeps the lowest matching channel.
+__global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const float* __restrict__ y,
+                              int* __restrict__ pos, Shape s) {
+    const long long total = static_cast<long long>(s.B) * s.CO * s.HW;
+    const int kpad = (s.CIg + 3) & ~3;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int stage = pos[i];
+        int result = (mode == 1) ? static_cast<int>(0xffffffffu) : 0;
+        if (stage >= 0) {
+            const int hw = static_cast<int>(i % s.HW);
+            const long long t = i / s.HW;
+            const int o = static_cast<int>(t % s.COg);
+            const long long t2 = t / s.COg;
+            const int g = static_cast<int>(t2 % s.G);
+            const long long m = (t2 / s.G) * s.HW + hw;
+            const float* ar = a0.ptr + m * a0.stride_row + g * a0.stride_group;
+            const float* ur = a1.ptr + m * a1.stride_row + g * a1.stride_group;
+            const float* br = b.ptr + o * b.stride_row + g * b.stride_group;
+            const float yv = y[i];
+            const int k0 = stage * 32;
+            float4 av[8], bv[8], uv[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int k = k0 + 4 * q;
+                const bool in = k < kpad;
+                av[q] = in ? *reinterpret_cast<const float4*>(ar + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                bv[q] = in ? *reinterpret_cast<const float4*>(br + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (mode != 0) uv[q] = in ? *reinterpret_cast<const float4*>(ur + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int q = 7; q >= 0; --q) {
+                const float ae[4] = {av[q].x, av[q].y, av[q].z, av[q].w};
+                const float be[4] = {bv[q].x, bv[q].y, bv[q].z, bv[q].w};
+                const float ue[4] = {uv[q].x, uv[q].y, uv[q].z, uv[q].w};
+#pragma unroll
+                for (int e = 3; e >= 0; --e) {
+                    const int k = k0 + 4 * q + e;
+                    bool hit, flag;
+                    if (mode == 0) {
+                        const float d = ae[e] - be[e];
+                        hit = fabsf(d) == yv;
+                        flag = d < 0.0f;
+                    } else {
+                        const float t1 = be[e] - ae[e], t2v = ue[e] - be[e];
+                        hit = (mode == 1) ? (fminf(t1, t2v) == -yv) : (fmaxf(t1, t2v) == yv);
+                        flag = !(t1 <= t2v);
+                    }
+                    if (hit && k < s.CIg) result = k | (flag ? static_cast<int>(0x80000000u) : 0);
+                }
+            }
+        }
+        pos[i] = result;
+    }
+}
+
 __global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
         float s = 0.0f;
@@ -172,6 +229,13 @@ int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
                     cudaStream_t st) {
     coef_gen_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, rinv, gcp, s, pitch);
+    LDN_LAUNCH_RET();
+}
+
+int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, int* pos, const Shape& s,
+                  cudaStream_t st) {
+    const long long total = static_cast<long long>(s.B) * s.CO * s.HW;
+    rescan_kernel<<<blocks_for(total), kBlock, 0, st>>>(mode, a0, a1, b, y, pos, s);
     LDN_LAUNCH_RET();
 }
 

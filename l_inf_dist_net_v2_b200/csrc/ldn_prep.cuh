@@ -23,6 +23,15 @@ int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
                     cudaStream_t st);
 
+// Second step of the forward kernels that save an index: `pos` holds, per output, the id of the 32-channel
+// stage in which the extremum was first reached (or -1); replace it by the channel index | flag.
+//   mode 0: p = inf value y = max |a - b|, flag = (a - b < 0)          (a1 unused; none: 0)
+//   mode 1: lower bound, y = -min(min(t1, t2)),  t1 = b - a0, t2 = a1 - b, flag = (t1 > t2)   (none: 0xffffffff)
+//   mode 2: upper bound, y = max(max(t1, t2)), same flag                (none: 0)
+// Operands are given as generic views (row / group strides in elements, reduction index contiguous).
+int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, int* pos, const Shape& s,
+                  cudaStream_t st);
+
 // grad_weight of the fused backward: gw[i] = -sum_t part[t * count + i], t < tiles
 int launch_side_reduce(const float* part, float* gw, long long count, int tiles, cudaStream_t st);
 

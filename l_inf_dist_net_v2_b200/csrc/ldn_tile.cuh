@@ -361,6 +361,13 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
             }
         }
 
+        if constexpr (Op::STAGE_HOOK) {
+#pragma unroll
+            for (int i = 0; i < kRegM; ++i)
+#pragma unroll
+                for (int j = 0; j < kRegN; ++j) Op::stage_end(accf[i][j], acci[i][j], kt);
+        }
+
         if (kt == KT - 1 || it == it1 - 1) {
             const bool whole = (seg_begin == tile * KT) && (kt == KT - 1);
             if (whole) {
