@@ -78,6 +78,28 @@ __global__ void coef_int_kernel(const float* __restrict__ go, const float* __res
     }
 }
 
+// flat fast paths (HW == 1, G == 1, pitch == COg: source and destination have the same element order)
+__global__ void coef_int_flat_kernel(const float4* __restrict__ go, const float4* __restrict__ y,
+                                     float4* __restrict__ coef, long long n4, int iq) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const float4 yv = y[i];
+        float4 v = go[i];
+        const float4 r = make_float4(1.0f / yv.x, 1.0f / yv.y, 1.0f / yv.z, 1.0f / yv.w);
+        for (int k = 0; k < iq; ++k) {
+            v.x *= r.x; v.y *= r.y; v.z *= r.z; v.w *= r.w;
+        }
+        coef[i] = v;
+    }
+}
+__global__ void coef_gen_flat_kernel(const float4* __restrict__ go, const float4* __restrict__ y,
+                                     float4* __restrict__ rinv, float4* __restrict__ gcp, long long n4) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const float4 yv = y[i];
+        rinv[i] = make_float4(1.0f / yv.x, 1.0f / yv.y, 1.0f / yv.z, 1.0f / yv.w);
+        gcp[i] = go[i];
+    }
+}
+
 __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ rinv,
                                 float* __restrict__ gcp, Shape s, int pitch) {
     const long long total = static_cast<long long>(s.G) * s.M * s.COg;
@@ -222,12 +244,32 @@ int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStr
     canon_w_kernel<<<blocks_for((long long)s.CO * s.CIg), kBlock, 0, st>>>(w, wc, s, pitch);
     LDN_LAUNCH_RET();
 }
+static bool flat_ok(const Shape& s, int pitch, const void* a, const void* b) {
+    return s.HW == 1 && s.G == 1 && pitch == s.COg && (s.COg & 3) == 0 &&
+           ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
+}
+
 int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, cudaStream_t st) {
+    if (flat_ok(s, pitch, go, y)) {
+        const long long n4 = static_cast<long long>(s.M) * s.COg / 4;
+        coef_int_flat_kernel<<<blocks_for(n4), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
+                                                              reinterpret_cast<const float4*>(y),
+                                                              reinterpret_cast<float4*>(coef), n4, iq);
+        LDN_LAUNCH_RET();
+    }
     coef_int_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, coef, s, pitch, iq);
     LDN_LAUNCH_RET();
 }
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
                     cudaStream_t st) {
+    if (flat_ok(s, pitch, go, y)) {
+        const long long n4 = static_cast<long long>(s.M) * s.COg / 4;
+        coef_gen_flat_kernel<<<blocks_for(n4), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
+                                                              reinterpret_cast<const float4*>(y),
+                                                              reinterpret_cast<float4*>(rinv),
+                                                              reinterpret_cast<float4*>(gcp), n4);
+        LDN_LAUNCH_RET();
+    }
     coef_gen_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, rinv, gcp, s, pitch);
     LDN_LAUNCH_RET();
 }

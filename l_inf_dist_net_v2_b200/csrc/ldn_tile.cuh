@@ -410,15 +410,17 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 }
 
 // Folds the partial accumulators of every tile that was shared between CTAs, in k order, and
-// finalises it.  Launched with one CTA per tile and the grid size of the main kernel as an argument;
-// CTAs of unshared tiles return at once.
+// finalises it.  Launched with kRegM CTAs per tile (CTA r of a tile handles register-row r of every
+// thread's block, i.e. 8 outputs per thread) and the grid size of the main kernel as an argument; CTAs
+// of unshared tiles return at once.
 template <class Op>
 __global__ void __launch_bounds__(kThreads)
 tile_fixup_kernel(const TileParams P, const int main_grid) {
     constexpr int NF = Op::NF;
     constexpr int NI = Op::NI;
     constexpr int NIA = NI > 0 ? NI : 1;
-    const long long tile = blockIdx.x;
+    const long long tile = blockIdx.x / kRegM;
+    const int i = blockIdx.x % kRegM;
     const int KT = P.kt;
     const long long t0 = tile * KT, t1 = t0 + KT;
     // CTA whose range contains iteration t0
@@ -429,12 +431,10 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
     const int tn = thread_col<Op>(tid);
     const int tm = thread_row<Op>(tid);
     const TileCoord tc = tile_coord(P, tile);
-    float accf[kRegM][kRegN][NF];
-    int acci[kRegM][kRegN][NIA];
+    float accf[kRegN][NF];
+    int acci[kRegN][NIA];
 #pragma unroll
-    for (int i = 0; i < kRegM; ++i)
-#pragma unroll
-        for (int j = 0; j < kRegN; ++j) Op::init(accf[i][j], acci[i][j]);
+    for (int j = 0; j < kRegN; ++j) Op::init(accf[j], acci[j]);
 
     for (; c < main_grid; ++c) {
         const long long b0 = range_begin(P.total_iters, main_grid, c);
@@ -443,31 +443,28 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
         if (b1 <= b0) continue;
         const int slot = (b0 / KT == tile) ? 0 : 1;
         const float* src = P.partials + (static_cast<size_t>(c) * 2 + slot) * (size_t)(NF + NI) * kTileElems;
-#pragma unroll
-        for (int i = 0; i < kRegM; ++i)
-#pragma unroll
-            for (int j = 0; j < kRegN; ++j) {
-                const int e = (i * kRegN + j) * kThreads + tid;
-                float pf[NF];
-                int pn[NIA];
-#pragma unroll
-                for (int a = 0; a < NF; ++a) pf[a] = src[a * kTileElems + e];
-#pragma unroll
-                for (int a = 0; a < NI; ++a) pn[a] = __float_as_int(src[(NF + a) * kTileElems + e]);
-                Op::combine(accf[i][j], acci[i][j], pf, pn);
-            }
-    }
-#pragma unroll
-    for (int i = 0; i < kRegM; ++i)
+        float pf[kRegN][NF];
+        int pn[kRegN][NIA];
 #pragma unroll
         for (int j = 0; j < kRegN; ++j) {
-            const int m = tc.m0 + own_index<Op::LA>(tm, i);
-            const int n = tc.n0 + own_index<Op::LB>(tn, j);
-            if (m < P.M && n < P.N) {
-                const float pr = Op::HAS_P ? Op::load_pres(P, m, n, tc.g) : 0.0f;
-                Op::finalize(accf[i][j], acci[i][j], pr, m, n, tc.g, P);
-            }
+            const int e = (i * kRegN + j) * kThreads + tid;
+#pragma unroll
+            for (int a = 0; a < NF; ++a) pf[j][a] = src[a * kTileElems + e];
+#pragma unroll
+            for (int a = 0; a < NI; ++a) pn[j][a] = __float_as_int(src[(NF + a) * kTileElems + e]);
         }
+#pragma unroll
+        for (int j = 0; j < kRegN; ++j) Op::combine(accf[j], acci[j], pf[j], pn[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kRegN; ++j) {
+        const int m = tc.m0 + own_index<Op::LA>(tm, i);
+        const int n = tc.n0 + own_index<Op::LB>(tn, j);
+        if (m < P.M && n < P.N) {
+            const float pr = Op::HAS_P ? Op::load_pres(P, m, n, tc.g) : 0.0f;
+            Op::finalize(accf[j], acci[j], pr, m, n, tc.g, P);
+        }
+    }
 }
 
 // Host launcher (ldn_launch.cuh provides the definition used by the .cu files).
@@ -495,7 +492,7 @@ int launch_tile(const TileLaunch& L, cudaStream_t stream) {
     const long long tiles = L.params.total_iters / L.params.kt;
     // a tile can only be shared when the ranges do not fall on tile boundaries
     if (L.params.total_iters % L.grid != 0 || (L.params.total_iters / L.grid) % L.params.kt != 0) {
-        tile_fixup_kernel<Op><<<static_cast<unsigned>(tiles), kThreads, 0, stream>>>(L.params, L.grid);
+        tile_fixup_kernel<Op><<<static_cast<unsigned>(tiles * kRegM), kThreads, 0, stream>>>(L.params, L.grid);
         e = cudaGetLastError();
         count_launches(1);
     }
