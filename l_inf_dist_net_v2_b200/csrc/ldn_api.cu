@@ -35,9 +35,10 @@ inline size_t canonical_floats(long long inner, long long rows, long long groups
     return static_cast<size_t>(ceil4(static_cast<int>(inner))) * rows * groups;
 }
 
-int build_map(CUtensorMap* map, const View& v, Layout layout) {
-    const unsigned bi = layout == Layout::RowMajor ? kTileK : kTileN;
-    const unsigned br = layout == Layout::RowMajor ? kTileM : kTileK;
+// `span` = rows (RowMajor) or columns (KMajor) of the tile: 128, or 64 for the B operand of narrow tiles
+int build_map(CUtensorMap* map, const View& v, Layout layout, int span = kTileM) {
+    const unsigned bi = layout == Layout::RowMajor ? kTileK : span;
+    const unsigned br = layout == Layout::RowMajor ? span : kTileK;
     unsigned long long dims[3], strides[2];
     unsigned box[3];
     dims[0] = v.inner;
@@ -133,16 +134,18 @@ int get_w_view(Call& c, const float* w, const Shape& s, View* v) {
 }
 
 // Common part of a tile-engine plan.
-int fill_plan(Call& c, TileLaunch* L, long long M, int N, int K, int G, int arrays) {
+int fill_plan(Call& c, TileLaunch* L, long long M, int N, int K, int G, int arrays, OpGeom geom = OpGeom{kTileN, 1}) {
     memset(L, 0, sizeof(*L));
     TileParams& P = L->params;
     P.M = static_cast<int>(M); P.N = N; P.K = K; P.G = G;
     P.tiles_m = static_cast<int>((M + kTileM - 1) / kTileM);
-    P.tiles_n = (N + kTileN - 1) / kTileN;
+    P.tiles_n = (N + geom.tile_n - 1) / geom.tile_n;
     P.kt = (K + kTileK - 1) / kTileK;
     P.total_iters = static_cast<long long>(G) * P.tiles_m * P.tiles_n * P.kt;
-    L->grid = static_cast<int>(P.total_iters < c.cap ? P.total_iters : c.cap);
-    P.partials = c.bump.take<float>(static_cast<size_t>(L->grid) * 2 * arrays * kTileElems);
+    const long long cap = static_cast<long long>(c.cap) * geom.ctas_per_sm;
+    L->grid = static_cast<int>(P.total_iters < cap ? P.total_iters : cap);
+    // (a narrow tile has half the outputs, and at most twice the CTAs: the slot size below is an upper bound)
+    P.partials = c.bump.take<float>(static_cast<size_t>(L->grid) * 2 * arrays * (kTileM * geom.tile_n));
     if (!P.partials) return kWorkspace;
     P.status = c.arena->status;
     P.trace = trace_buffer();
@@ -163,7 +166,9 @@ OutAddr w_addr(const Shape& s) {
 int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, const View& wv, const Shape& s,
                 float* out0, float* out1, int* outi0, int* outi1, const float* pres, float p) {
     TileLaunch L;
-    int r = fill_plan(c, &L, s.M, s.COg, s.CIg, s.G, fwd_acc_arrays(kind));
+    OpGeom geom{kTileN, 1};
+    if (kind == FwdKind::PowInt || kind == FwdKind::PowGen || kind == FwdKind::PowNorm) geom = fwd_pow_geom(kind, ip);
+    int r = fill_plan(c, &L, s.M, s.COg, s.CIg, s.G, fwd_acc_arrays(kind), geom);
     if (r != kOk) return r;
     TileParams& P = L.params;
     P.a_row_coord = a0.row_coord;
@@ -177,7 +182,7 @@ int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, c
     P.p = p; P.q = p - 1.0f;
     if ((r = build_map(&L.map_a0, a0, Layout::RowMajor)) != kOk) return r;
     if ((r = build_map(&L.map_a1, a1 ? *a1 : a0, Layout::RowMajor)) != kOk) return r;
-    if ((r = build_map(&L.map_b, wv, Layout::RowMajor)) != kOk) return r;
+    if ((r = build_map(&L.map_b, wv, Layout::RowMajor, geom.tile_n)) != kOk) return r;
     switch (kind) {
         case FwdKind::PowInt:
         case FwdKind::PowGen:

@@ -2,6 +2,12 @@
 #include "ldn_ops.cuh"
 
 namespace ldn {
+OpGeom fwd_pow_geom(FwdKind kind, int) {
+    if (kind == FwdKind::PowNorm) return geom_of<FwdPowNorm>();
+    if (kind == FwdKind::PowGen) return geom_of<FwdPowGen>();
+    return geom_of<FwdPowInt<8>>();
+}
+
 int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st) {
     if (kind == FwdKind::PowGen) return launch_tile<FwdPowGen>(L, st);
     if (kind == FwdKind::PowNorm) return launch_tile<FwdPowNorm>(L, st);

@@ -19,6 +19,17 @@ inline int fwd_acc_arrays(FwdKind k) {
 }
 inline int fwd_num_a(FwdKind k) { return (k == FwdKind::Bound || k == FwdKind::BoundPosLower || k == FwdKind::BoundPosUpper) ? 2 : 1; }
 
+// tile width and resident CTAs per SM of the kernel a launch function will pick
+struct OpGeom {
+    int tile_n;
+    int ctas_per_sm;
+};
+template <class Op>
+constexpr OpGeom geom_of() {
+    return OpGeom{16 * Op::REG_N, Op::CTAS_PER_SM};
+}
+OpGeom fwd_pow_geom(FwdKind kind, int ip);
+
 int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st);   // PowInt (ip 1..8), PowGen, PowNorm
 int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper}
 int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st);                   // iq 0..8, or -1 for general p

@@ -190,6 +190,8 @@ struct FwdLayout {
     static constexpr bool FUSED_W = false;
     static constexpr bool STAGE_HOOK = false;  // op has a stage_end(f, n, stage) step after every 32-wide stage
     static constexpr int STAGES = kStages;
+    static constexpr int REG_N = 8;        // output columns per thread: 8 (128 x 128 tile) or 4 (128 x 64)
+    static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -464,6 +466,8 @@ struct BwdLayout {
     static constexpr bool FUSED_W = false;
     static constexpr bool STAGE_HOOK = false;
     static constexpr int STAGES = kStages;
+    static constexpr int REG_N = 8;
+    static constexpr int CTAS_PER_SM = 1;
     static constexpr bool HAS_P = true;
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
         return P.pres.ptr[n + m * P.pres.stride_row + g * P.pres.stride_group];

@@ -25,22 +25,25 @@ enum class Layout { RowMajor, KMajor };
 
 constexpr int kStages = 4;  // default depth of the operand ring (Op::STAGES)
 
-template <Layout L>
+// R = number of rows / columns a thread owns in that dimension (8, or 4 for the narrow 128 x 64 tile)
+template <Layout L, int R = 8>
 __device__ __forceinline__ int own_index(int t, int r) {
     if (L == Layout::RowMajor) return t + 16 * r;
+    if (R == 4) return t * 4 + r;
     return (r >> 2) * 64 + t * 4 + (r & 3);
 }
 
 // Fetch the 8 x KS register slab (8 owned rows/cols x KS consecutive k, KS in {1, 2, 4}) of one operand
 // tile for k-group `ps` (k = ps * KS .. ps * KS + KS - 1 inside the 32-wide stage).
-template <Layout L, int KS>
-__device__ __forceinline__ void fetch_slab(const char* tile, int t, int ps, float (&v)[8][KS]) {
+template <Layout L, int KS, int R>
+__device__ __forceinline__ void fetch_slab(const char* tile, int t, int ps, float (&v)[R][KS]) {
+    static_assert(R == 8 || R == 4, "a thread owns 8 or 4 rows / columns");
     static_assert(KS == 1 || KS == 2 || KS == 4, "k-step must be 1, 2 or 4");
     if (L == Layout::RowMajor) {
         const int k = ps * KS;
         const int off = (((k >> 2) ^ (t & 7)) << 4) + ((k & 3) << 2);
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
+        for (int r = 0; r < R; ++r) {
             const char* src = tile + (t + 16 * r) * 128 + off;
             if constexpr (KS == 4) {
                 const float4 x = *reinterpret_cast<const float4*>(src);
@@ -55,11 +58,14 @@ __device__ __forceinline__ void fetch_slab(const char* tile, int t, int ps, floa
     } else {
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk) {
-            const char* row = tile + (ps * KS + kk) * 512 + t * 16;
+            // a k-major tile row holds 16 * R floats
+            const char* row = tile + (ps * KS + kk) * (R * 64) + t * 16;
             const float4 lo = *reinterpret_cast<const float4*>(row);
-            const float4 hi = *reinterpret_cast<const float4*>(row + 256);
             v[0][kk] = lo.x; v[1][kk] = lo.y; v[2][kk] = lo.z; v[3][kk] = lo.w;
-            v[4][kk] = hi.x; v[5][kk] = hi.y; v[6][kk] = hi.z; v[7][kk] = hi.w;
+            if constexpr (R == 8) {
+                const float4 hi = *reinterpret_cast<const float4*>(row + 256);
+                v[4][kk] = hi.x; v[5][kk] = hi.y; v[6][kk] = hi.z; v[7][kk] = hi.w;
+            }
         }
     }
 }
@@ -68,13 +74,13 @@ struct TileCoord {
     int g, m0, n0;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(const TileParams& P, long long tile) {
+__device__ __forceinline__ TileCoord tile_coord(const TileParams& P, long long tile, int tile_n) {
     TileCoord c;
     const int per_group = P.tiles_m * P.tiles_n;
     c.g = static_cast<int>(tile / per_group);
     const int r = static_cast<int>(tile - static_cast<long long>(c.g) * per_group);
     c.m0 = (r % P.tiles_m) * kTileM;
-    c.n0 = (r / P.tiles_m) * kTileN;
+    c.n0 = (r / P.tiles_m) * tile_n;
     return c;
 }
 
@@ -106,13 +112,14 @@ constexpr int kSideBufferBytes = kTileK * kTileN * 4;  // column sums of one sta
 
 template <class Op>
 struct TileSmem {
-    static constexpr int kStage = (Op::NUM_A + 1) * kOperandTileBytes;
+    static constexpr int kTileN = 16 * Op::REG_N;
+    static constexpr int kStage = Op::NUM_A * kOperandTileBytes + kTileN * kTileK * 4;
     static constexpr int kSide = Op::FUSED_W ? 2 * kSideBufferBytes : 0;
     static constexpr int kTotal = Op::STAGES * kStage + kSide + 1024 /*alignment slack*/ + 64 /*barriers*/;
 };
 
 template <class Op>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, Op::CTAS_PER_SM)
 tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
             const __grid_constant__ CUtensorMap map_b, const TileParams P) {
     constexpr int NA = Op::NUM_A;
@@ -121,6 +128,10 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     constexpr int NIA = NI > 0 ? NI : 1;
     constexpr int STAGE = TileSmem<Op>::kStage;
     constexpr int STAGES = Op::STAGES;
+    constexpr int RN = Op::REG_N;          // output columns per thread
+    constexpr int TN = 16 * RN;            // output columns per tile
+    constexpr int TELEMS = kTileM * TN;    // outputs per tile
+    static_assert(!Op::FUSED_W || RN == 8, "the fused backward uses the 128 x 128 tile");
 
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -152,7 +163,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     auto issue = [&](long long it, int ls) {
         const long long tile = it / KT;
         const int kt = static_cast<int>(it - tile * KT);
-        const TileCoord tc = tile_coord(P, tile);
+        const TileCoord tc = tile_coord(P, tile, TN);
         char* st = smem + (ls % STAGES) * STAGE;
         uint64_t* bar = &full[ls % STAGES];
         mbar_expect_tx(bar, STAGE);
@@ -184,7 +195,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     auto flush_side = [&](long long it_done, int buf) {
         const long long tile_d = it_done / KT;
         const int kt_d = static_cast<int>(it_done - tile_d * KT);
-        const TileCoord cd = tile_coord(P, tile_d);
+        const TileCoord cd = tile_coord(P, tile_d, TN);
         float* src = side + buf * (kTileK * kTileN);
         float* dst_tile = P.side_out + (static_cast<size_t>(cd.m0 / kTileM) * P.G + cd.g) * (size_t)P.K * P.N;
         const bool vec = (P.N & 3) == 0;
@@ -211,9 +222,9 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         }
     };
 
-    float accf[kRegM][kRegN][NF];
-    int acci[kRegM][kRegN][NIA];
-    float pres[kRegM][kRegN];
+    float accf[kRegM][RN][NF];
+    int acci[kRegM][RN][NIA];
+    float pres[kRegM][RN];
     TileCoord tc = {0, 0, 0};
     long long seg_begin = it0;
     const long long first_tile = it0 / KT;
@@ -224,15 +235,15 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         const int kt = static_cast<int>(it - tile * KT);
         if (it == it0 || kt == 0) {
             seg_begin = it;
-            tc = tile_coord(P, tile);
+            tc = tile_coord(P, tile, TN);
 #pragma unroll
             for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                for (int j = 0; j < kRegN; ++j) {
+                for (int j = 0; j < RN; ++j) {
                     Op::init(accf[i][j], acci[i][j]);
                     if (Op::HAS_P) {
                         const int m = tc.m0 + own_index<Op::LA>(tm, i);
-                        const int n = tc.n0 + own_index<Op::LB>(tn, j);
+                        const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
                         pres[i][j] = (m < P.M && n < P.N) ? Op::load_pres(P, m, n, tc.g) : 0.0f;
                     } else {
                         pres[i][j] = 0.0f;
@@ -264,13 +275,13 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         // order: no swap there, at the price of a 2-way conflict on their narrow RowMajor reads)
         const int perm = (KS < 4 && !Op::FUSED_W) ? (tn >> 3) : 0;
         struct Slab {
-            float a0[8][KS], a1[8][KS], b[8][KS];
+            float a0[8][KS], a1[8][KS], b[RN][KS];
         };
         auto load = [&](Slab& sl, int ks) {
             const int ps = ks ^ perm;
-            fetch_slab<Op::LA, KS>(sa0, tm, ps, sl.a0);
-            if (NA == 2) fetch_slab<Op::LA, KS>(sa1, tm, ps, sl.a1);
-            fetch_slab<Op::LB, KS>(sb, tn, ps, sl.b);
+            fetch_slab<Op::LA, KS, 8>(sa0, tm, ps, sl.a0);
+            if (NA == 2) fetch_slab<Op::LA, KS, 8>(sa1, tm, ps, sl.a1);
+            fetch_slab<Op::LB, KS, RN>(sb, tn, ps, sl.b);
         };
         auto compute = [&](const Slab& sl, int ks) {
             const int ps = ks ^ perm;
@@ -283,13 +294,13 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 float* buf = side + (ls & 1) * (kTileK * kTileN);
 #pragma unroll
                 for (int k = 0; k < KS; ++k) {
-                    float2 col[kRegN / 2];
+                    float2 col[RN / 2];
 #pragma unroll
-                    for (int jp = 0; jp < kRegN / 2; ++jp) col[jp] = make_float2(0.0f, 0.0f);
+                    for (int jp = 0; jp < RN / 2; ++jp) col[jp] = make_float2(0.0f, 0.0f);
 #pragma unroll
                     for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                        for (int jp = 0; jp < kRegN / 2; ++jp) {
+                        for (int jp = 0; jp < RN / 2; ++jp) {
                             const float2 term = Op::term_pair(pres[i][2 * jp], pres[i][2 * jp + 1], sl.a0[i][k],
                                                               NA == 2 ? sl.a1[i][k] : 0.0f, sl.b[2 * jp][k],
                                                               sl.b[2 * jp + 1][k], i + jp + k, P);
@@ -327,7 +338,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                    for (int j = 0; j < kRegN; j += 2)
+                    for (int j = 0; j < RN; j += 2)
                         Op::template update_pair<KS>(accf[i][j][0], accf[i][j + 1][0], pres[i][j], pres[i][j + 1],
                                                      sl.a0[i], NA == 2 ? sl.a1[i] : sl.a0[i], sl.b[j], sl.b[j + 1],
                                                      i + (j >> 1), P);
@@ -335,7 +346,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                    for (int j = 0; j < kRegN; ++j)
+                    for (int j = 0; j < RN; ++j)
                         Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], sl.a0[i],
                                                 NA == 2 ? sl.a1[i] : sl.a0[i], sl.b[j], chunk, i + j, P);
             }
@@ -365,7 +376,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                for (int j = 0; j < kRegN; ++j) Op::stage_end(accf[i][j], acci[i][j], kt);
+                for (int j = 0; j < RN; ++j) Op::stage_end(accf[i][j], acci[i][j], kt);
         }
 
         if (kt == KT - 1 || it == it1 - 1) {
@@ -374,24 +385,24 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                 for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                    for (int j = 0; j < kRegN; ++j) {
+                    for (int j = 0; j < RN; ++j) {
                         const int m = tc.m0 + own_index<Op::LA>(tm, i);
-                        const int n = tc.n0 + own_index<Op::LB>(tn, j);
+                        const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
                         if (m < P.M && n < P.N) Op::finalize(accf[i][j], acci[i][j], pres[i][j], m, n, tc.g, P);
                     }
             } else {
                 const int slot = (tile == first_tile) ? 0 : 1;
                 float* dst = P.partials +
-                             (static_cast<size_t>(blockIdx.x) * 2 + slot) * (size_t)(NF + NI) * kTileElems;
+                             (static_cast<size_t>(blockIdx.x) * 2 + slot) * (size_t)(NF + NI) * TELEMS;
 #pragma unroll
                 for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                    for (int j = 0; j < kRegN; ++j) {
-                        const int e = (i * kRegN + j) * kThreads + tid;
+                    for (int j = 0; j < RN; ++j) {
+                        const int e = (i * RN + j) * kThreads + tid;
 #pragma unroll
-                        for (int a = 0; a < NF; ++a) dst[a * kTileElems + e] = accf[i][j][a];
+                        for (int a = 0; a < NF; ++a) dst[a * TELEMS + e] = accf[i][j][a];
 #pragma unroll
-                        for (int a = 0; a < NI; ++a) dst[(NF + a) * kTileElems + e] = __int_as_float(acci[i][j][a]);
+                        for (int a = 0; a < NI; ++a) dst[(NF + a) * TELEMS + e] = __int_as_float(acci[i][j][a]);
                     }
             }
         }
@@ -419,6 +430,9 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
     constexpr int NF = Op::NF;
     constexpr int NI = Op::NI;
     constexpr int NIA = NI > 0 ? NI : 1;
+    constexpr int RN = Op::REG_N;
+    constexpr int TN = 16 * RN;
+    constexpr int TELEMS = kTileM * TN;
     const long long tile = blockIdx.x / kRegM;
     const int i = blockIdx.x % kRegM;
     const int KT = P.kt;
@@ -430,11 +444,11 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
     const int tid = threadIdx.x;
     const int tn = thread_col<Op>(tid);
     const int tm = thread_row<Op>(tid);
-    const TileCoord tc = tile_coord(P, tile);
-    float accf[kRegN][NF];
-    int acci[kRegN][NIA];
+    const TileCoord tc = tile_coord(P, tile, TN);
+    float accf[RN][NF];
+    int acci[RN][NIA];
 #pragma unroll
-    for (int j = 0; j < kRegN; ++j) Op::init(accf[j], acci[j]);
+    for (int j = 0; j < RN; ++j) Op::init(accf[j], acci[j]);
 
     for (; c < main_grid; ++c) {
         const long long b0 = range_begin(P.total_iters, main_grid, c);
@@ -442,24 +456,24 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
         if (b0 >= t1) break;
         if (b1 <= b0) continue;
         const int slot = (b0 / KT == tile) ? 0 : 1;
-        const float* src = P.partials + (static_cast<size_t>(c) * 2 + slot) * (size_t)(NF + NI) * kTileElems;
-        float pf[kRegN][NF];
-        int pn[kRegN][NIA];
+        const float* src = P.partials + (static_cast<size_t>(c) * 2 + slot) * (size_t)(NF + NI) * TELEMS;
+        float pf[RN][NF];
+        int pn[RN][NIA];
 #pragma unroll
-        for (int j = 0; j < kRegN; ++j) {
-            const int e = (i * kRegN + j) * kThreads + tid;
+        for (int j = 0; j < RN; ++j) {
+            const int e = (i * RN + j) * kThreads + tid;
 #pragma unroll
-            for (int a = 0; a < NF; ++a) pf[j][a] = src[a * kTileElems + e];
+            for (int a = 0; a < NF; ++a) pf[j][a] = src[a * TELEMS + e];
 #pragma unroll
-            for (int a = 0; a < NI; ++a) pn[j][a] = __float_as_int(src[(NF + a) * kTileElems + e]);
+            for (int a = 0; a < NI; ++a) pn[j][a] = __float_as_int(src[(NF + a) * TELEMS + e]);
         }
 #pragma unroll
-        for (int j = 0; j < kRegN; ++j) Op::combine(accf[j], acci[j], pf[j], pn[j]);
+        for (int j = 0; j < RN; ++j) Op::combine(accf[j], acci[j], pf[j], pn[j]);
     }
 #pragma unroll
-    for (int j = 0; j < kRegN; ++j) {
+    for (int j = 0; j < RN; ++j) {
         const int m = tc.m0 + own_index<Op::LA>(tm, i);
-        const int n = tc.n0 + own_index<Op::LB>(tn, j);
+        const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
         if (m < P.M && n < P.N) {
             const float pr = Op::HAS_P ? Op::load_pres(P, m, n, tc.g) : 0.0f;
             Op::finalize(accf[j], acci[j], pr, m, n, tc.g, P);
