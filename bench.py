@@ -55,6 +55,10 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--ci", type=int, default=3072)
     ap.add_argument("--co", type=int, default=5120)
+    ap.add_argument("--workload", default="layer", choices=["layer", "mlp-train", "mlp-certify"],
+                    help="layer: the headline single-layer step (default); mlp-train / mlp-certify: extra end-to-end "
+                         "steps of a 6-layer distance MLP (depth 6, width 5120, 3x32x32 inputs, 10 classes)")
+    ap.add_argument("--certify-samples", type=int, default=50000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     return ap.parse_args()
@@ -395,6 +399,139 @@ def run_ours(args, rank, world, local_rank):
 
 
 # ------------------------------------------------------------------------------------------------
+# Extra workloads: a 6-layer distance MLP built from this package's modules, with the layer sizes, initialisation,
+# loss and margin computation of the reference's MLPModel recipe (ell_inf_models.py:16-46, main.py:304-310)
+# ------------------------------------------------------------------------------------------------
+def build_mlp(depth, width, pixels, classes, p, device):
+    import l_inf_dist_net_v2_b200 as ldn
+    torch.manual_seed(0)
+    layers = [ldn.NormDist(pixels, width, bias=False, mean_shift=True, std=1.0, identity_val=10.0)]
+    for _ in range(depth - 2):
+        layers.append(ldn.NormDist(width, width, bias=False, mean_shift=True, std=1.0, identity_val=10.0))
+    layers.append(ldn.NormDist(width, classes, bias=True, mean_shift=False, std=1.0, identity_val=10.0))
+    net = torch.nn.ModuleList(layers).to(device)
+    for m in net:
+        m.p = p
+    return net
+
+
+def mlp_forward(net, x, lower=None, upper=None):
+    paras = (x, lower, upper)
+    for m in net:
+        paras = m(*paras)
+    return paras
+
+
+def hinge_loss(outputs, lower, upper, targets, eps, mix=0.25):
+    # margins of the negated distances: upper bound of the others minus lower bound of the target
+    x, lo, up = -outputs, -upper, -lower
+    margin = up - torch.gather(lo, 1, targets.view(-1, 1))
+    margin = margin.scatter(1, targets.view(-1, 1), 0) / (2 * eps)
+    res = margin.clamp(min=0)
+    return (1 - mix) * res.max(dim=1)[0].mean() + mix * res.mean()
+
+
+def run_mlp(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
+    from l_inf_dist_net_v2_b200._lib import lib
+    from l_inf_dist_net_v2_b200.parallel import allreduce_mean_
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    train = args.workload == "mlp-train"
+    p = p_value(args.p) if train else math.inf
+    B = args.batch
+    net = build_mlp(6, 5120, 3072, 10, p, dev)
+    gen = torch.Generator().manual_seed(1000 + rank)
+    eps = 8.0 / 255.0
+    sampler = ClockSampler(local_rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    if train:
+        xh = torch.rand(B, 3, 32, 32, generator=gen).pin_memory()
+        th = torch.randint(0, 10, (B,), generator=gen).pin_memory()
+        x_dev = torch.empty(B, 3072, device=dev)
+        t_dev = torch.empty(B, dtype=torch.long, device=dev)
+        opt = torch.optim.SGD(net.parameters(), lr=0.02)
+        params = [q for q in net.parameters()]
+        net.train()
+        loss_h = torch.zeros(1).pin_memory()
+
+        def step():
+            x_dev.copy_(xh.view(B, -1), non_blocking=True)
+            t_dev.copy_(th, non_blocking=True)
+            opt.zero_grad(set_to_none=True)
+            out, _, _ = mlp_forward(net, x_dev)
+            loss = hinge_loss(out, out - eps, out + eps, t_dev, eps)
+            loss.backward()
+            if world > 1:
+                allreduce_mean_([q.grad for q in params if q.grad is not None])
+            opt.step()
+            loss_h.copy_(loss.detach().view(1), non_blocking=True)
+
+        per_step_samples = B
+        h2d, d2h = xh.numel() * 4 + th.numel() * 8, 4
+    else:
+        n_local = args.certify_samples // world
+        batches = (n_local + B - 1) // B
+        xh = torch.rand(B, 3, 32, 32, generator=gen).pin_memory()
+        x_dev = torch.empty(B, 3072, device=dev)
+        net.eval()
+        res_h = torch.zeros(B, 10).pin_memory()
+
+        def step():  # one certification batch: value and interval bounds through all six layers
+            x_dev.copy_(xh.view(B, -1), non_blocking=True)
+            with torch.no_grad():
+                out, lo, up = mlp_forward(net, x_dev, (x_dev - eps).clamp(min=0), (x_dev + eps).clamp(max=1))
+            res_h.copy_(lo, non_blocking=True)
+
+        per_step_samples = B
+        h2d, d2h = xh.numel() * 4, res_h.numel() * 4
+        args.steps = min(args.steps, batches) if args.steps else batches
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    barrier()
+    sampler.start()
+    launches0 = lib.ldn_kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    launches = int(lib.ldn_kernel_launches() - launches0)
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    C.check_status()
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank != 0:
+        return None
+    value = world * per_step_samples * args.steps / (ms * 1e-3)
+    name = "mlp_train_samples_per_s" if train else "mlp_certify_samples_per_s"
+    return {"metric": name, "value": round(value, 1), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": ("6-layer distance MLP (3072-5120x5-10) training step, p=%s, hinge loss, SGD lr 0.02, "
+                                    "batch %d per rank" % (args.p, B)) if train else
+                                   ("6-layer distance MLP certification (value + interval bounds, eps=8/255), p=inf, "
+                                    "batch %d per rank" % B),
+                       "batch_per_rank": B, "l2": "working set 560 MB of weights per step, larger than L2"},
+            "e2e": {"value": round(value, 1), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "l_inf_dist_net_v2_b200 modules + autograd + torch.optim.SGD"},
+            "gpu_launches": launches, "clocks": clocks}
+
+
+# ------------------------------------------------------------------------------------------------
 # CPU baseline / reference arm: the reference's CPU torch path (oracle/torch_port.py)
 # ------------------------------------------------------------------------------------------------
 def _cpu_sample(args, rows, cols):
@@ -532,7 +669,7 @@ def main():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             torch.cuda.set_device(local_rank)
             dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        line = run_ours(args, rank, world, local_rank)
+        line = run_ours(args, rank, world, local_rank) if args.workload == "layer" else run_mlp(args, rank, world, local_rank)
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
