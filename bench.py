@@ -59,6 +59,10 @@ def parse_args():
                     help="layer: the headline single-layer step (default); mlp-train / mlp-certify: extra end-to-end "
                          "steps of a 6-layer distance MLP (depth 6, width 5120, 3x32x32 inputs, 10 classes)")
     ap.add_argument("--certify-samples", type=int, default=50000)
+    ap.add_argument("--overlap-sms", type=int, default=0,
+                    help="mlp-train with N > 1: start each parameter's all-reduce as soon as its gradient is ready and "
+                         "keep this many SMs free of the persistent tile kernels during backward so that the "
+                         "collective can run beside them (0: all-reduce after backward)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     return ap.parse_args()
@@ -109,7 +113,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [s.strip() for s in line.split(",")]
             if len(parts) >= 7:
-                self.samples.append(parts)
+                self.samples.append((time.time(), parts))
+
+    def mark(self):
+        """Start of the timed region: only samples taken from here on are summarised (if there are any)."""
+        self.t_mark = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -121,7 +129,13 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        window = [p for (t, p) in self.samples if t >= getattr(self, "t_mark", 0.0)]
+        scope = "timed region"
+        if not window:
+            window = [p for (_, p) in self.samples]
+            scope = "warm-up and timed region (no sample fell inside the timed region)"
+        self.scope = scope
+        for s in window:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -132,7 +146,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm),
+                "scope": self.scope}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -244,12 +259,13 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- timed region: device-resident ----------------------------------------------------------
     sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         flush()
         step()
     torch.cuda.synchronize()
     barrier()
-    sampler.start()
+    sampler.mark()
     launches0 = lib.ldn_kernel_launches()
     torch.cuda.synchronize()
     t_wall0 = time.perf_counter()
@@ -460,6 +476,13 @@ def run_mlp(args, rank, world, local_rank):
         params = [q for q in net.parameters()]
         net.train()
         loss_h = torch.zeros(1).pin_memory()
+        overlap = world > 1 and args.overlap_sms > 0
+        pending = []
+        if overlap:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            for q in params:
+                q.register_post_accumulate_grad_hook(
+                    lambda prm: pending.append(dist.all_reduce(prm.grad, async_op=True)))
 
         def step():
             x_dev.copy_(xh.view(B, -1), non_blocking=True)
@@ -467,9 +490,18 @@ def run_mlp(args, rank, world, local_rank):
             opt.zero_grad(set_to_none=True)
             out, _, _ = mlp_forward(net, x_dev)
             loss = hinge_loss(out, out - eps, out + eps, t_dev, eps)
-            loss.backward()
-            if world > 1:
-                allreduce_mean_([q.grad for q in params if q.grad is not None])
+            if overlap:
+                lib.ldn_set_max_ctas(sms - args.overlap_sms)
+                loss.backward()
+                lib.ldn_set_max_ctas(0)
+                for h in pending:
+                    h.wait()
+                pending.clear()
+                torch._foreach_div_([q.grad for q in params if q.grad is not None], world)
+            else:
+                loss.backward()
+                if world > 1:
+                    allreduce_mean_([q.grad for q in params if q.grad is not None])
             opt.step()
             loss_h.copy_(loss.detach().view(1), non_blocking=True)
 
@@ -493,11 +525,12 @@ def run_mlp(args, rank, world, local_rank):
         h2d, d2h = xh.numel() * 4, res_h.numel() * 4
         args.steps = min(args.steps, batches) if args.steps else batches
 
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
     barrier()
-    sampler.start()
+    sampler.mark()
     launches0 = lib.ldn_kernel_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
