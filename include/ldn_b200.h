@@ -75,7 +75,8 @@ LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer);
 /*
  * Pipe-throughput probe for roofline denominators (no counterpart in the reference).  kind 0 runs a loop
  * of independent FFMA chains, kind 2 the same chains issued as packed fma.rn.f32x2, kind 1 a loop of
- * independent ex2(lg2(x)) chains, `iters` iterations, on
+ * independent ex2(lg2(x)) chains, kind 3 eight such MUFU chains beside eight packed-FMA chains (16 FMAs per step;
+ * *lane_ops then counts the MUFU operations only), `iters` iterations, on
  * 8 CTAs of 256 threads per SM.  *lane_ops receives the number of lane operations the launch executes
  * (FFMAs, respectively MUFU operations); the caller times the launch.  sink: one device float.
  */

@@ -30,6 +30,20 @@ __global__ void __launch_bounds__(kProbeThreads) probe_kernel(int iters, float s
         for (int i = 0; i < kProbeIlp; ++i) {
             if (KIND == 0) {
                 v[i] = fmaf(v[i], a, b);
+            } else if (KIND == 3) {
+                // mixed: chains 0..7 are MUFU (lg2 then ex2), chains 8..15 each run 8 packed FMAs per step
+                if (i < 8) {
+                    float l, e;
+                    asm volatile("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(v[i]));
+                    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(l));
+                    v[i] = e;
+                } else if ((i & 1) == 0) {
+                    float2 r = make_float2(v[i], v[i + 1]);
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) r = __ffma2_rn(r, make_float2(a, a), make_float2(b, b));
+                    v[i] = r.x;
+                    v[i + 1] = r.y;
+                }
             } else if (KIND == 2) {
                 // packed FP32: one instruction, two lane operations; chains pair up (i, i ^ 1)
                 if ((i & 1) == 0) {
@@ -62,7 +76,7 @@ LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer) { g_trace =
 LDN_API unsigned long long ldn_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream) {
-    if (!sink || !lane_ops || iters <= 0 || (kind < 0 || kind > 2)) return kBadArgument;
+    if (!sink || !lane_ops || iters <= 0 || (kind < 0 || kind > 3)) return kBadArgument;
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
@@ -70,9 +84,12 @@ LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long*
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (kind == 0) probe_kernel<0><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
     else if (kind == 2) probe_kernel<2><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
+    else if (kind == 3) probe_kernel<3><<<blocks, kProbeThreads, 0, st>>>(iters, 1.5f, sink);
     else probe_kernel<1><<<blocks, kProbeThreads, 0, st>>>(iters, 1.5f, sink);
-    // kinds 0 and 2: one FMA lane operation per chain step; kind 1: two MUFU operations per chain step
-    *lane_ops = static_cast<unsigned long long>(blocks) * kProbeThreads * iters * kProbeIlp * (kind == 1 ? 2 : 1);
+    // kinds 0 and 2: one FMA lane operation per chain step; kind 1: two MUFU operations per chain step;
+    // kind 3: 8 of the 16 chains are MUFU chains (two operations per step), only those are counted
+    const unsigned long long per_step = kind == 1 ? 2ull * kProbeIlp : (kind == 3 ? 16ull : 1ull * kProbeIlp);
+    *lane_ops = static_cast<unsigned long long>(blocks) * kProbeThreads * iters * per_step;
     count_launches(1);
     return cuda_status(cudaGetLastError());
 }
