@@ -559,10 +559,11 @@ struct BwdFusedInt : BwdLayout<false> {
     static constexpr bool PACKED = true;
     static constexpr bool FUSED_W = true;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
+    // term = coef * returned value
     __device__ static float2 term_pair(float p0, float p1, float c, float, float b0, float b1, int,
-                                       const TileParams&) {
-        const float2 sp = signed_pow2<IQ>(pk_sub(make_float2(p0, p1), make_float2(b0, b1)));
-        return __fmul2_rn(sp, make_float2(c, c));
+                                       const TileParams&, float2& coef) {
+        coef = make_float2(c, c);
+        return signed_pow2<IQ>(pk_sub(make_float2(p0, p1), make_float2(b0, b1)));
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
@@ -578,11 +579,12 @@ struct BwdFusedGen : BwdLayout<false> {
     static constexpr int STAGES = 3;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     __device__ static float2 term_pair(float p0, float p1, float r, float gr, float b0, float b1, int sel,
-                                       const TileParams& P) {
+                                       const TileParams& P, float2& coef) {
         const float2 t = pk_sub(make_float2(p0, p1), make_float2(b0, b1));
         const float2 l = make_float2(lg2_approx(fabsf(t.x) * r), lg2_approx(fabsf(t.y) * r));
         const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__fmul2_rn(make_float2(P.q, P.q), l), sel);
-        return make_float2(gr * copysignf(v.x, t.x), gr * copysignf(v.y, t.y));
+        coef = make_float2(gr, gr);
+        return make_float2(copysignf(v.x, t.x), copysignf(v.y, t.y));
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {

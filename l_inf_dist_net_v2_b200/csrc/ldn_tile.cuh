@@ -301,14 +301,16 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                     for (int i = 0; i < kRegM; ++i)
 #pragma unroll
                         for (int jp = 0; jp < RN / 2; ++jp) {
-                            const float2 term = Op::term_pair(pres[i][2 * jp], pres[i][2 * jp + 1], sl.a0[i][k],
+                            // term = coef * base, folded into both accumulations as one FMA each
+                            float2 coef;
+                            const float2 base = Op::term_pair(pres[i][2 * jp], pres[i][2 * jp + 1], sl.a0[i][k],
                                                               NA == 2 ? sl.a1[i][k] : 0.0f, sl.b[2 * jp][k],
-                                                              sl.b[2 * jp + 1][k], i + jp + k, P);
+                                                              sl.b[2 * jp + 1][k], i + jp + k, P, coef);
                             const float2 acc =
-                                __fadd2_rn(make_float2(accf[i][2 * jp][0], accf[i][2 * jp + 1][0]), term);
+                                __ffma2_rn(base, coef, make_float2(accf[i][2 * jp][0], accf[i][2 * jp + 1][0]));
                             accf[i][2 * jp][0] = acc.x;
                             accf[i][2 * jp + 1][0] = acc.y;
-                            col[jp] = __fadd2_rn(col[jp], term);
+                            col[jp] = __ffma2_rn(base, coef, col[jp]);
                         }
                     // Sum over the 16 row groups of the warp (lane bits 0..3) with a halving butterfly:
                     // each exchange step passes on half of the values a lane still holds, so 8 values need
