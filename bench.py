@@ -55,9 +55,10 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--ci", type=int, default=3072)
     ap.add_argument("--co", type=int, default=5120)
-    ap.add_argument("--workload", default="layer", choices=["layer", "mlp-train", "mlp-certify"],
+    ap.add_argument("--workload", default="layer", choices=["layer", "mlp-train", "mlp-certify", "hybrid-train", "hybrid-certify"],
                     help="layer: the headline single-layer step (default); mlp-train / mlp-certify: extra end-to-end "
-                         "steps of a 6-layer distance MLP (depth 6, width 5120, 3x32x32 inputs, 10 classes)")
+                         "steps of a 6-layer distance MLP (depth 6, width 5120, 3x32x32 inputs, 10 classes); "
+                         "hybrid-*: 5 distance layers (width 5120) + interval-bound linear head (hidden 512)")
     ap.add_argument("--certify-samples", type=int, default=50000)
     ap.add_argument("--overlap-sms", type=int, default=0,
                     help="mlp-train with N > 1: start each parameter's all-reduce as soon as its gradient is ready and "
@@ -487,6 +488,34 @@ def mlp_forward(net, x, lower=None, upper=None):
     return paras
 
 
+class IntervalHead(torch.nn.Module):
+    """Interval-bound head of the reference's HybridModel (ell_inf_models.py:49-75 with BoundLinear, BoundTanh,
+    BoundFinalLinear of core/modules/basic_modules.py:27-46, :16-18, :77-101), written in centre / radius form:
+    a scaled linear layer maps centre c and radius r to (W c + b, |W| r); tanh is monotone; the last layer
+    returns, per sample, the worst-case logit differences against the target class."""
+
+    def __init__(self, width, hidden, classes):
+        super().__init__()
+        self.w1 = torch.nn.Parameter(torch.randn(hidden, width))
+        self.b1 = torch.nn.Parameter(torch.zeros(hidden))
+        self.w2 = torch.nn.Parameter(torch.randn(classes, hidden))
+        self.b2 = torch.nn.Parameter(torch.zeros(classes))
+        self.s1, self.s2 = 1.0 / math.sqrt(width), 1.0 / math.sqrt(hidden)
+
+    def forward(self, x, lower, upper, targets):
+        centre, radius = (lower + upper) * 0.5, (upper - lower) * 0.5
+        h = torch.addmm(self.b1, x, self.w1.t(), alpha=self.s1)
+        hc = torch.addmm(self.b1, centre, self.w1.t(), alpha=self.s1)
+        hr = torch.mm(radius, self.w1.abs().t()) * self.s1
+        h, hl, hu = torch.tanh(h), torch.tanh(hc - hr), torch.tanh(hc + hr)
+        logits = torch.addmm(self.b2, h, self.w2.t(), alpha=self.s2)
+        dw = self.w2.unsqueeze(0) - self.w2.index_select(0, targets).unsqueeze(1)      # B x classes x hidden
+        db = self.b2.unsqueeze(0) - self.b2.index_select(0, targets).unsqueeze(1)      # B x classes
+        c2, r2 = (hl + hu) * 0.5, (hu - hl) * 0.5
+        worst = (dw.bmm(c2.unsqueeze(-1)) + dw.abs().bmm(r2.unsqueeze(-1))).squeeze(-1) * self.s2 + db
+        return logits, worst
+
+
 def hinge_loss(outputs, lower, upper, targets, eps, mix=0.25):
     # margins of the negated distances: upper bound of the others minus lower bound of the target
     x, lo, up = -outputs, -upper, -lower
@@ -504,10 +533,18 @@ def run_mlp(args, rank, world, local_rank):
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    train = args.workload == "mlp-train"
+    train = args.workload.endswith("train")
+    hybrid = args.workload.startswith("hybrid")
     p = p_value(args.p) if train else math.inf
     B = args.batch
-    net = build_mlp(6, 5120, 3072, 10, p, dev)
+    if hybrid:
+        # five distance layers 3072 -> 5120 -> ... -> 5120, all with mean shift and without bias
+        net = build_mlp(6, 5120, 3072, 5120, p, dev)[:5]
+        torch.manual_seed(1)
+        head = IntervalHead(5120, 512, 10).to(dev)
+    else:
+        net = build_mlp(6, 5120, 3072, 10, p, dev)
+        head = None
     gen = torch.Generator().manual_seed(1000 + rank)
     eps = 8.0 / 255.0
     sampler = ClockSampler(local_rank)
@@ -521,8 +558,9 @@ def run_mlp(args, rank, world, local_rank):
         th = torch.randint(0, 10, (B,), generator=gen).pin_memory()
         x_dev = torch.empty(B, 3072, device=dev)
         t_dev = torch.empty(B, dtype=torch.long, device=dev)
-        opt = torch.optim.SGD(net.parameters(), lr=0.02)
-        params = [q for q in net.parameters()]
+        params = [q for q in net.parameters()] + ([q for q in head.parameters()] if hybrid else [])
+        opt = torch.optim.SGD(params, lr=0.02)
+        eps_train = 0.0345
         net.train()
         loss_h = torch.zeros(1).pin_memory()
         overlap = world > 1 and args.overlap_sms > 0
@@ -538,7 +576,11 @@ def run_mlp(args, rank, world, local_rank):
             t_dev.copy_(th, non_blocking=True)
             opt.zero_grad(set_to_none=True)
             out, _, _ = mlp_forward(net, x_dev)
-            loss = hinge_loss(out, out - eps, out + eps, t_dev, eps)
+            if hybrid:
+                _, worst = head(out, out - eps_train, out + eps_train, t_dev)
+                loss = torch.nn.functional.cross_entropy(worst, t_dev)
+            else:
+                loss = hinge_loss(out, out - eps, out + eps, t_dev, eps)
             if overlap:
                 lib.ldn_set_max_ctas(sms - args.overlap_sms)
                 loss.backward()
@@ -560,14 +602,19 @@ def run_mlp(args, rank, world, local_rank):
         n_local = args.certify_samples // world
         batches = (n_local + B - 1) // B
         xh = torch.rand(B, 3, 32, 32, generator=gen).pin_memory()
+        th = torch.randint(0, 10, (B,), generator=gen).pin_memory()
         x_dev = torch.empty(B, 3072, device=dev)
+        t_dev = torch.empty(B, dtype=torch.long, device=dev)
         net.eval()
         res_h = torch.zeros(B, 10).pin_memory()
 
-        def step():  # one certification batch: value and interval bounds through all six layers
+        def step():  # one certification batch: value and interval bounds through every distance layer
             x_dev.copy_(xh.view(B, -1), non_blocking=True)
+            t_dev.copy_(th, non_blocking=True)
             with torch.no_grad():
                 out, lo, up = mlp_forward(net, x_dev, (x_dev - eps).clamp(min=0), (x_dev + eps).clamp(max=1))
+                if hybrid:
+                    _, lo = head(out, lo, up, t_dev)
             res_h.copy_(lo, non_blocking=True)
 
         per_step_samples = B
@@ -599,14 +646,17 @@ def run_mlp(args, rank, world, local_rank):
     if rank != 0:
         return None
     value = world * per_step_samples * args.steps / (ms * 1e-3)
-    name = "mlp_train_samples_per_s" if train else "mlp_certify_samples_per_s"
+    name = args.workload.replace("-", "_") + "_samples_per_s"
+    model = ("5 distance layers (3072-5120x5) + interval-bound head 5120-512-10" if hybrid
+             else "6-layer distance MLP (3072-5120x5-10)")
+    loss_name = "cross-entropy on worst-case logits, eps_train 0.0345" if hybrid else "hinge loss"
     return {"metric": name, "value": round(value, 1), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": ("6-layer distance MLP (3072-5120x5-10) training step, p=%s, hinge loss, SGD lr 0.02, "
-                                    "batch %d per rank" % (args.p, B)) if train else
-                                   ("6-layer distance MLP certification (value + interval bounds, eps=8/255), p=inf, "
-                                    "batch %d per rank" % B),
+            "config": {"workload": ("%s training step, p=%s, %s, SGD lr 0.02, batch %d per rank"
+                                    % (model, args.p, loss_name, B)) if train else
+                                   ("%s certification (value + interval bounds, eps=8/255), p=inf, batch %d per rank"
+                                    % (model, B)),
                        "batch_per_rank": B, "l2": "working set 560 MB of weights per step, larger than L2"},
             "e2e": {"value": round(value, 1), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "l_inf_dist_net_v2_b200 modules + autograd + torch.optim.SGD"},
