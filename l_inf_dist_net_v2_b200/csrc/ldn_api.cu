@@ -94,7 +94,7 @@ inline int cap_for(const DeviceCtx* ctx) {
 }
 
 // The x operand as the engine reads it: the caller's array when it is fully connected (HW == 1) with a
-// 16-byte aligned base and row length, else a canonical copy [g][m][pitch] made by `copy`.
+// 16-byte aligned base and row length, else a canonical copy [g][m][pitch].
 bool x_is_natural(const float* x, const Shape& s) { return s.HW == 1 && s.CIg % 4 == 0 && aligned16(x); }
 View x_natural_view(const float* x, const Shape& s) {
     if (s.G == 1) return View{x, s.CIg, s.M, 1, s.CI, s.M * s.CI, 1};

@@ -33,7 +33,6 @@ constexpr int kRegM = 8;
 constexpr int kRegN = 8;
 constexpr int kTileElems = kTileM * kTileN;            // outputs per tile
 constexpr int kOperandTileBytes = kTileM * kTileK * 4;  // 16 KiB, both operand tile shapes
-constexpr int kMaxAccArrays = 4;                        // float + int accumulator arrays per output
 
 // Bounded waits: a poll loop gives up after this many failed polls (each followed by a short
 // nanosleep once the fast polls are used up), writes kDeviceTimeout into the status word and the

@@ -50,6 +50,39 @@ __global__ void canon_bounds_kernel(const float* __restrict__ xl, const float* _
     }
 }
 
+// HW > 1: tiled transpose through shared memory.  Source rows (b, g, c, :) are contiguous in hw, destination
+// rows (g, m = b HW + hw, :) are contiguous in c; a 32 x 32 tile makes both sides coalesced.  grid = (ceil(HW/32),
+// ceil(CIg/32), B*G).  With `second` non-null the pair (x, second) is treated as interval bounds and sanitised.
+__global__ void canon_transpose_kernel(const float* __restrict__ x, const float* __restrict__ second,
+                                       float* __restrict__ xc, float* __restrict__ sc, Shape s, int pitch) {
+    __shared__ float t0[32][33], t1[32][33];
+    const int bg = blockIdx.z, b = bg / s.G, g = bg % s.G;
+    const int hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const float* src = x + (static_cast<long long>(bg) * s.CIg) * s.HW;
+    const float* src2 = second ? second + (static_cast<long long>(bg) * s.CIg) * s.HW : nullptr;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int c = c0 + r, hw = hw0 + threadIdx.x;
+        if (c < s.CIg && hw < s.HW) {
+            float lo = src[static_cast<long long>(c) * s.HW + hw];
+            if (src2) {
+                float up = src2[static_cast<long long>(c) * s.HW + hw];
+                if (lo > up) lo = up = (lo + up) * 0.5f;
+                t1[r][threadIdx.x] = up;
+            }
+            t0[r][threadIdx.x] = lo;
+        }
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int hw = hw0 + r, c = c0 + threadIdx.x;
+        if (c < s.CIg && hw < s.HW) {
+            const long long dst = (static_cast<long long>(g) * s.M + static_cast<long long>(b) * s.HW + hw) * pitch + c;
+            xc[dst] = t0[threadIdx.x][r];
+            if (src2) sc[dst] = t1[threadIdx.x][r];
+        }
+    }
+}
+
 __global__ void canon_w_kernel(const float* __restrict__ w, float* __restrict__ wc, Shape s, int pitch) {
     const long long total = static_cast<long long>(s.CO) * s.CIg;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -231,12 +264,29 @@ __global__ void bound_scatter_kernel(const float* __restrict__ gol, const float*
         return cuda_status(cudaGetLastError()); \
     } while (0)
 
+static bool transpose_grid(const Shape& s, dim3* grid) {
+    const long long bg = static_cast<long long>(s.B) * s.G;
+    if (s.HW < 8 || bg > 65535 || (s.CIg + 31) / 32 > 65535) return false;
+    *grid = dim3((s.HW + 31) / 32, (s.CIg + 31) / 32, static_cast<unsigned>(bg));
+    return true;
+}
+
 int launch_canon_x(const float* x, float* xc, const Shape& s, int pitch, cudaStream_t st) {
+    dim3 grid;
+    if (transpose_grid(s, &grid)) {
+        canon_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(x, nullptr, xc, nullptr, s, pitch);
+        LDN_LAUNCH_RET();
+    }
     canon_x_kernel<<<blocks_for((long long)s.G * s.M * s.CIg), kBlock, 0, st>>>(x, xc, s, pitch);
     LDN_LAUNCH_RET();
 }
 int launch_canon_bounds(const float* xl, const float* xu, float* lc, float* uc, const Shape& s, int pitch,
                         cudaStream_t st) {
+    dim3 grid;
+    if (transpose_grid(s, &grid)) {
+        canon_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(xl, xu, lc, uc, s, pitch);
+        LDN_LAUNCH_RET();
+    }
     canon_bounds_kernel<<<blocks_for((long long)s.G * s.M * s.CIg), kBlock, 0, st>>>(xl, xu, lc, uc, s, pitch);
     LDN_LAUNCH_RET();
 }

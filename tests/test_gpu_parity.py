@@ -165,6 +165,7 @@ SHAPES = [
     (6, 36, 20, 2, 5),
     (5, 48, 264, 1, 49),
     (300, 260, 10, 1, 1),
+    (4, 70, 24, 2, 64),
 ]
 
 
