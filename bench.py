@@ -401,8 +401,8 @@ def run_ours(args, rank, world, local_rank):
             rows.append(row)
         return rows
 
-    # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised in
-    # profiles/tile_kernel_p8_512x3072x5120.md; only valid for that shape and p
+    # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
+    # under profiles/; only valid for that shape and p
     ncu_traffic = {}
     if (B, CI, CO, args.p) == (512, 3072, 5120, "8"):
         ncu_traffic = {"forward": 76.8e6, "backward_fused": 405.0e6}

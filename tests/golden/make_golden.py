@@ -1,7 +1,7 @@
 """Generate tests/golden/ref_fallback.npz from the upstream reference's own pure-torch path.
 
-Run once in a container that has the upstream checkout (default /root/reference, override with
-LDN_REFERENCE_ROOT):   python tests/golden/make_golden.py
+Run once in a container that has the upstream checkout (its location can be given in the environment
+variable LDN_REFERENCE_ROOT):   python tests/golden/make_golden.py
 
 What it records, per case, are the inputs and the outputs of the reference functions
 `core.norm_dist.norm_dist(..., use_custom_cuda_func=False)` and
