@@ -66,6 +66,14 @@ LDN_API void ldn_set_max_ctas(int max_ctas);
 LDN_API unsigned long long ldn_kernel_launches(void);
 
 /*
+ * Per-kernel timing (no counterpart in the reference): while enabled, every launch of a tile kernel is bracketed by
+ * a CUDA-event pair on its stream; ldn_last_tile_kernel_ms waits for the latest pair and returns the duration of that
+ * one kernel in milliseconds (-1 if nothing was recorded).  One pair per process: use from one thread, one device.
+ */
+LDN_API void ldn_enable_kernel_timing(int enabled);
+LDN_API float ldn_last_tile_kernel_ms(void);
+
+/*
  * Tracing hook (no counterpart in the reference): while a non-null device buffer is set, every CTA of every
  * tile-engine launch writes four 64-bit words at buffer[4 * cta]: SM id, start and end time (globaltimer, ns)
  * and its number of k-steps.  The buffer must hold 4 * (number of SMs) words; pass NULL to switch it off.

@@ -187,6 +187,10 @@ inline size_t pad256(size_t bytes) { return (bytes + 255) & ~size_t(255); }
 int make_tensor_map(CUtensorMap* map, const float* base, const unsigned long long dims[3],
                     const unsigned long long strides_elems[2], const unsigned box[3], bool swizzle128);
 
+// optional CUDA-event pair around the most recent tile-kernel launch (ldn_diag.cu); no-ops unless enabled
+void timing_before(cudaStream_t st);
+void timing_after(cudaStream_t st);
+
 // host-side launch counter and optional per-CTA trace buffer (ldn_diag.cu)
 unsigned long long* trace_buffer();
 void count_launches(int n);

@@ -13,6 +13,21 @@ void count_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long
 unsigned long long* g_trace = nullptr;
 unsigned long long* trace_buffer() { return g_trace; }
 
+// Event pair around the latest tile-kernel launch, for per-kernel roofline numbers.
+bool g_timing = false;
+cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
+void timing_before(cudaStream_t st) {
+    if (!g_timing) return;
+    if (!g_ev0) {
+        cudaEventCreate(&g_ev0);
+        cudaEventCreate(&g_ev1);
+    }
+    cudaEventRecord(g_ev0, st);
+}
+void timing_after(cudaStream_t st) {
+    if (g_timing && g_ev1) cudaEventRecord(g_ev1, st);
+}
+
 namespace {
 constexpr int kProbeThreads = 256;
 constexpr int kProbeIlp = 16;
@@ -72,6 +87,16 @@ using namespace ldn;
 extern "C" {
 
 LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer) { g_trace = device_buffer; }
+
+LDN_API void ldn_enable_kernel_timing(int enabled) { g_timing = enabled != 0; }
+
+LDN_API float ldn_last_tile_kernel_ms(void) {
+    if (!g_ev0 || !g_ev1) return -1.0f;
+    if (cudaEventSynchronize(g_ev1) != cudaSuccess) return -1.0f;
+    float ms = -1.0f;
+    if (cudaEventElapsedTime(&ms, g_ev0, g_ev1) != cudaSuccess) return -1.0f;
+    return ms;
+}
 
 LDN_API unsigned long long ldn_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 

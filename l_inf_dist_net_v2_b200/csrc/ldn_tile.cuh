@@ -501,7 +501,9 @@ int launch_tile(const TileLaunch& L, cudaStream_t stream) {
         if (e != cudaSuccess) return cuda_status(e);
         configured[dev] = true;
     }
+    timing_before(stream);
     tile_kernel<Op><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b, L.params);
+    timing_after(stream);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_status(e);
     count_launches(1);

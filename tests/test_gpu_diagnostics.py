@@ -87,3 +87,17 @@ def test_release_scratch_then_reuse(lib):
     torch.cuda.synchronize()
     assert torch.equal(y1, y2)
     C.check_status()
+
+
+def test_kernel_timing_hook(lib):
+    from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
+    x = torch.rand(256, 512, 1, device="cuda")
+    w = torch.randn(512, 512, device="cuda")
+    y = torch.empty(256, 512, 1, device="cuda")
+    lib.ldn_enable_kernel_timing(1)
+    try:
+        C.norm_dist_forward(x, w, y, 1, 8.0)
+        ms = lib.ldn_last_tile_kernel_ms()
+    finally:
+        lib.ldn_enable_kernel_timing(0)
+    assert 0.0 < ms < 50.0
