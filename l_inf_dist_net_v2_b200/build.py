@@ -74,5 +74,44 @@ def build(force=False, verbose=False):
     return LIB
 
 
+EXT_NAME = "_norm_dist_ext"
+EXT_SRC = os.path.join(CSRC, "binding", "norm_dist_ext.cpp")
+
+
+def ext_path():
+    import sysconfig
+    return os.path.join(PKG, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_extension(force=False, verbose=False):
+    """Compiles the pybind11 / PyTorch binding (csrc/binding/norm_dist_ext.cpp) against libldn_b200.so, in-tree.
+    Plain g++ with the include and library paths torch reports; no GPU needed."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    out = ext_path()
+    deps = [EXT_SRC, os.path.join(ROOT, "include", "ldn_b200.h")]
+    if not force and not _stale(out, deps):
+        return out
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           "-DTORCH_EXTENSION_NAME=" + EXT_NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch.compiled_with_cxx11_abi())]
+    for inc in ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(cuda_home, "include"),
+                                    os.path.join(ROOT, "include")]:
+        cmd += ["-isystem" if "torch" in inc or "python" in inc else "-I", inc]
+    cmd += [EXT_SRC, "-o", out, "-L", torch_lib, "-L", PKG, "-lldn_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu",
+            "-ltorch_cuda", "-ltorch", "-ltorch_python", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("building the PyTorch binding failed")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--no-ext" not in sys.argv:
+        print(build_extension(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

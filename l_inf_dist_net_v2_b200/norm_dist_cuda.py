@@ -5,7 +5,8 @@ Same names, same argument order, same in-place semantics (the caller allocates e
 returned) and the same checks: every tensor must be a contiguous CUDA tensor (core/cuda/norm_dist.cpp:8-10)
 of dtype float32 (int32 for pos arrays).  Shapes are read from the tensors exactly as the reference
 wrappers do (core/cuda/norm_dist.cpp:44,73,127).  Differences: kernels are launched on the current
-stream of the tensors' device instead of the legacy default stream, and a failing launch raises.
+stream of the tensors' device instead of the legacy default stream, and a failing launch raises
+(RuntimeError).
 """
 import torch
 
@@ -153,3 +154,17 @@ def bound_inf_dist_backward_input_weight(grad_outputL, grad_outputU, posL, posU,
 def check_status():
     """Waits for the current stream and raises if a kernel reported a bounded-wait timeout."""
     check(lib.ldn_check_status(_stream()), "device status check")
+
+
+# The compiled pybind11 / PyTorch binding of the same C ABI (csrc/binding/norm_dist_ext.cpp, built in-tree by
+# build.py) replaces the ctypes wrappers above when it is present: same names, same checks, less call overhead.
+# Both bindings call the same library; neither computes anything itself.
+BINDING = "ctypes"
+try:
+    from . import _norm_dist_ext as _ext
+except ImportError:
+    _ext = None
+if _ext is not None:
+    for _name in __all__ + ["check_status"]:
+        globals()[_name] = getattr(_ext, _name)
+    BINDING = "pybind11"

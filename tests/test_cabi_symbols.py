@@ -76,3 +76,11 @@ def test_module_parameter_names_and_identity_init():
     wv = conv.weight.view(8, 2, 3, 3)
     for i in range(8):
         assert wv[i, i % 2, 1, 1].item() == -5.0
+
+
+def test_compiled_binding_is_used_when_built():
+    import os
+    from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
+    pkg = os.path.dirname(C.__file__)
+    built = any(f.startswith("_norm_dist_ext") and f.endswith(".so") for f in os.listdir(pkg))
+    assert C.BINDING == ("pybind11" if built else "ctypes")

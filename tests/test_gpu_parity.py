@@ -298,13 +298,12 @@ def test_forward_with_max(C):
 
 
 def test_bad_arguments_raise_before_launch(C):
-    from l_inf_dist_net_v2_b200._lib import LdnError
     x = torch.rand(2, 6, 1, device="cuda")
     w = torch.randn(3, 6, device="cuda")
     y = torch.empty(2, 3, 1, device="cuda")
-    with pytest.raises(LdnError):
+    with pytest.raises(RuntimeError, match="status 1"):
         C.norm_dist_forward(x, w, y, 1, -1.0)
-    with pytest.raises(LdnError):
+    with pytest.raises(RuntimeError, match="status 1"):
         C.norm_dist_forward(x, w, y, 4, 8.0)  # CI not divisible by G
     with pytest.raises(RuntimeError, match="contiguous"):
         C.norm_dist_forward(x.transpose(0, 1), w, y, 1, 8.0)
