@@ -15,7 +15,8 @@
  *   - the caller allocates every output; outputs need not be zeroed, the library zero-fills wherever
  *     it accumulates;
  *   - pos arrays have the layout of y; bit 31 is a flag, bits 0..30 the channel index in the group.
- * Sizes are 32-bit per dimension but all offsets are computed in 64 bits.
+ * Sizes are 32-bit per dimension but all offsets are computed in 64 bits.  An empty batch (B == 0 or HW == 0) is a
+ * successful no-op: nothing is launched, a weight gradient is set to zero.
  *
  * Scratch: kernels that need intermediate device memory take it from a per-(device, stream) arena that
  * the library allocates on first use and grows on demand (cudaMalloc; a growth synchronises the stream).

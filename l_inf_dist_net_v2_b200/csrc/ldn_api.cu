@@ -57,14 +57,27 @@ int build_map(CUtensorMap* map, const View& v, Layout layout, int span = kTileM)
 
 inline Operand as_operand(const View& v) { return Operand{v.ptr, v.stride_row, v.stride_group}; }
 
+// internal: the batch (or the spatial extent) is empty -- nothing to compute, like the reference, whose
+// kernels then run with every row masked off
+constexpr int kEmptyBatch = -1;
+
 int check_shape(int B, int CO, int CI, int G, int HW, Shape* s) {
-    if (B <= 0 || CO <= 0 || CI <= 0 || G <= 0 || HW <= 0) return kBadArgument;
+    if (B < 0 || CO <= 0 || CI <= 0 || G <= 0 || HW < 0) return kBadArgument;
     if (CI % G != 0 || CO % G != 0) return kBadArgument;
+    if (B == 0 || HW == 0) return kEmptyBatch;
     s->B = B; s->CO = CO; s->CI = CI; s->G = G; s->HW = HW;
     s->CIg = CI / G; s->COg = CO / G;
     s->M = static_cast<long long>(B) * HW;
     if (s->M > 0x7fffffffLL) return kBadArgument;
     return kOk;
+}
+
+// Result of a call on an empty batch: outputs with a batch dimension are empty; a weight gradient is a sum
+// over no samples, i.e. zero.
+int empty_result(float* grad_weight, int CO, int CI, int G, ldn_stream_t stream) {
+    if (!grad_weight) return kOk;
+    return cuda_status(cudaMemsetAsync(grad_weight, 0, sizeof(float) * static_cast<size_t>(CO) * (CI / G),
+                                       reinterpret_cast<cudaStream_t>(stream)));
 }
 
 struct Call {
@@ -377,6 +390,7 @@ LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B
                           float* output, float p, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!input || !weight || !output) return kBadArgument;
     if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
@@ -408,6 +422,7 @@ LDN_API int ldn_norm_dist_forward_with_max(const float* input, const float* weig
                                    ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!input || !weight || !max_output || !output) return kBadArgument;
     if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
@@ -427,6 +442,7 @@ LDN_API int ldn_norm_dist_backward_input(const float* grad_output, const float* 
                                  float* grad_input, float p, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!grad_input) return kBadArgument;
     return norm_dist_backward(grad_output, input, weight, output, s, grad_input, nullptr, p, stream);
@@ -437,6 +453,7 @@ LDN_API int ldn_norm_dist_backward_input_weight(const float* grad_output, const 
                                         float* grad_input, float* grad_weight, float p, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(grad_weight, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!grad_weight) return kBadArgument;
     return norm_dist_backward(grad_output, input, weight, output, s, grad_input, grad_weight, p, stream);
@@ -446,6 +463,7 @@ LDN_API int ldn_inf_dist_forward_nograd(const float* input, const float* weight,
                                 float* output, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     return inf_forward(input, weight, s, output, nullptr, stream);
 }
@@ -454,6 +472,7 @@ LDN_API int ldn_inf_dist_forward(const float* input, const float* weight, int B,
                          float* output, int* pos, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!pos) return kBadArgument;
     return inf_forward(input, weight, s, output, pos, stream);
@@ -463,6 +482,7 @@ LDN_API int ldn_inf_dist_backward_input(const float* grad_output, const int* pos
                                 float* grad_input, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!grad_output || !pos || !grad_input) return kBadArgument;
     return launch_inf_scatter(grad_output, pos, grad_input, nullptr, s, reinterpret_cast<cudaStream_t>(stream));
@@ -472,6 +492,7 @@ LDN_API int ldn_inf_dist_backward_input_weight(const float* grad_output, const i
                                        int HW, float* grad_input, float* grad_weight, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(grad_weight, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!grad_output || !pos || !grad_weight) return kBadArgument;
     return launch_inf_scatter(grad_output, pos, grad_input, grad_weight, s, reinterpret_cast<cudaStream_t>(stream));
@@ -482,6 +503,7 @@ LDN_API int ldn_bound_inf_dist_forward_nograd(const float* inputL, const float* 
                                       ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     return bound_forward(inputL, inputU, weight, s, outputL, outputU, nullptr, nullptr, stream);
 }
@@ -491,6 +513,7 @@ LDN_API int ldn_bound_inf_dist_forward(const float* inputL, const float* inputU,
                                int* posL, int* posU, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!posL || !posU) return kBadArgument;
     return bound_forward(inputL, inputU, weight, s, outputL, outputU, posL, posU, stream);
@@ -501,6 +524,7 @@ LDN_API int ldn_bound_inf_dist_backward_input(const float* grad_outputL, const f
                                       float* grad_inputL, float* grad_inputU, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!grad_outputL || !grad_outputU || !posL || !posU || !grad_inputL || !grad_inputU) return kBadArgument;
     return launch_bound_scatter(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, nullptr, s,
@@ -513,6 +537,7 @@ LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, 
                                              ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(grad_weight, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!grad_outputL || !grad_outputU || !posL || !posU || !grad_inputL || !grad_inputU || !grad_weight)
         return kBadArgument;
@@ -567,6 +592,7 @@ LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float*
                                                 int G, int HW, float* output, ldn_stream_t stream) {
     Shape s;
     int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     if (!input || !weight || !output) return kBadArgument;
     Call c;

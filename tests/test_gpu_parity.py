@@ -490,3 +490,21 @@ def test_against_reference_cuda_kernels(C, shape):
         assert rel_to_max(gx.cpu().numpy(), gxr.cpu().numpy()) < tol, (shape, p)
         assert rel_to_max(gw.cpu().numpy(), gwr.cpu().numpy()) < tol, (shape, p)
     C.check_status()
+
+
+def test_empty_batch_is_a_no_op(C):
+    # like the reference, whose kernels run with every row masked off: empty outputs, zero weight gradient
+    w = torch.randn(6, 8, device="cuda")
+    x = torch.empty(0, 8, 1, device="cuda")
+    y = torch.empty(0, 6, 1, device="cuda")
+    pos = torch.empty(0, 6, 1, device="cuda", dtype=torch.int32)
+    C.norm_dist_forward(x, w, y, 1, 8.0)
+    C.inf_dist_forward(x, w, y, pos, 1)
+    C.bound_inf_dist_forward_nograd(x, x, w, y, y.clone(), 1)
+    gw = torch.full_like(w, float("nan"))
+    C.norm_dist_backward_input_weight(y, x, w, y, torch.empty_like(x), gw, 1, 8.0)
+    assert torch.all(gw == 0)
+    gw.fill_(float("nan"))
+    C.inf_dist_backward_input_weight(y, pos, torch.empty_like(x), gw, 1)
+    assert torch.all(gw == 0)
+    C.check_status()
