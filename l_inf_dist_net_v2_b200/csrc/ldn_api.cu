@@ -221,7 +221,10 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     const int cap = cap_for(ctx);
     const int iq = int_power(p - 1.0f);
     const int ncoef = iq >= 0 ? 1 : 2;
-    const size_t coef_floats = canonical_floats(s.COg, s.M, s.G);
+    // general p: coefficient arrays padded to whole tiles (see launch_coef_gen)
+    const long long coef_rows = iq >= 0 ? s.M : (s.M + kTileM - 1) / kTileM * kTileM;
+    const long long coef_pitch = iq >= 0 ? ceil4(s.COg) : (s.COg + kTileK - 1) / kTileK * kTileK;
+    const size_t coef_floats = static_cast<size_t>(coef_pitch) * coef_rows * s.G;
     // Both gradients wanted: one fused kernel evaluates every term once (grad_input accumulators plus
     // per-row-tile column sums for grad_weight).  It needs tiles_m copies of grad_weight as scratch, so very
     // tall problems (conv layouts with many rows) keep the two-kernel path; so does p = 1 (constant terms).
@@ -238,17 +241,19 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     float* c0 = c.bump.take<float>(coef_floats);
     float* c1 = ncoef == 2 ? c.bump.take<float>(coef_floats) : nullptr;
     if (!c0 || (ncoef == 2 && !c1)) return kWorkspace;
-    const View cv0 = canonical_view(c0, s.COg, s.M, s.G);
-    const View cv1 = canonical_view(c1 ? c1 : c0, s.COg, s.M, s.G);
-    if (iq >= 0) r = launch_coef_int(go, y, c0, s, static_cast<int>(cv0.stride_row), iq, c.st);
-    else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(cv0.stride_row), c.st);
+    const long long coef_inner = iq >= 0 ? s.COg : coef_pitch;
+    const View cv0 = View{c0, coef_inner, coef_rows, s.G, coef_pitch, coef_rows * coef_pitch, 1};
+    const View cv1 = View{c1 ? c1 : c0, coef_inner, coef_rows, s.G, coef_pitch, coef_rows * coef_pitch, 1};
+    if (iq >= 0) r = launch_coef_int(go, y, c0, s, static_cast<int>(coef_pitch), iq, c.st);
+    else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(coef_pitch), coef_rows, p - 1.0f, c.st);
     if (r != kOk) return r;
 
     if (fused) {
         float* side = c.bump.take<float>(side_floats);
         if (!side) return kWorkspace;
         TileLaunch L;
-        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1)) != kOk) return r;
+        const OpGeom geom = bwd_fused_geom(iq);
+        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom)) != kOk) return r;
         TileParams& P = L.params;
         P.a_row_coord = cv0.row_coord;
         P.b_row_coord = wv.row_coord;
@@ -260,14 +265,15 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
         P.p = p; P.q = p - 1.0f;
         if ((r = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return r;
         if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_b, wv, Layout::KMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n)) != kOk) return r;
         if ((r = launch_bwd_fused(iq, L, c.st)) != kOk) return r;
         return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m), c.st);
     }
     if (gx) {
         // out (m = (b, hw), n = c), k = o
         TileLaunch L;
-        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1)) != kOk) return r;
+        const OpGeom geom = bwd_x_geom(iq);
+        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom)) != kOk) return r;
         TileParams& P = L.params;
         P.a_row_coord = cv0.row_coord;
         P.b_row_coord = wv.row_coord;
@@ -278,13 +284,14 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
         P.p = p; P.q = p - 1.0f;
         if ((r = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return r;
         if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_b, wv, Layout::KMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n)) != kOk) return r;
         if ((r = launch_bwd_x(iq, L, c.st)) != kOk) return r;
     }
     if (gw) {
         // out (m = o, n = c), k = (b, hw)
         TileLaunch L;
-        if ((r = fill_plan(c, &L, s.COg, s.CIg, static_cast<int>(s.M), s.G, 1)) != kOk) return r;
+        const OpGeom geom = bwd_w_geom(iq);
+        if ((r = fill_plan(c, &L, s.COg, s.CIg, static_cast<int>(s.M), s.G, 1, geom)) != kOk) return r;
         TileParams& P = L.params;
         P.a_row_coord = cv0.row_coord;
         P.b_row_coord = xv.row_coord;
@@ -295,7 +302,7 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
         P.p = p; P.q = p - 1.0f;
         if ((r = build_map(&L.map_a0, cv0, Layout::KMajor)) != kOk) return r;
         if ((r = build_map(&L.map_a1, cv1, Layout::KMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_b, xv, Layout::KMajor)) != kOk) return r;
+        if ((r = build_map(&L.map_b, xv, Layout::KMajor, geom.tile_n)) != kOk) return r;
         if ((r = launch_bwd_w(iq, L, c.st)) != kOk) return r;
     }
     return kOk;

@@ -2,6 +2,8 @@
 #include "ldn_ops.cuh"
 
 namespace ldn {
+OpGeom bwd_fused_geom(int iq) { return iq >= 1 ? geom_of<BwdFusedInt<7>>() : geom_of<BwdFusedGen>(); }
+
 int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st) {
     switch (iq) {
         case 1: return launch_tile<BwdFusedInt<1>>(L, st);

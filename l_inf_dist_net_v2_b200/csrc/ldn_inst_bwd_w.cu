@@ -2,6 +2,8 @@
 #include "ldn_ops.cuh"
 
 namespace ldn {
+OpGeom bwd_w_geom(int iq) { return iq >= 0 ? geom_of<BwdPowInt<7, true>>() : geom_of<BwdPowGen<true>>(); }
+
 int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st) {
     switch (iq) {
         case 0: return launch_tile<BwdPowInt<0, true>>(L, st);

@@ -2,6 +2,8 @@
 #include "ldn_ops.cuh"
 
 namespace ldn {
+OpGeom bwd_x_geom(int iq) { return iq >= 0 ? geom_of<BwdPowInt<7, false>>() : geom_of<BwdPowGen<false>>(); }
+
 int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st) {
     switch (iq) {
         case 0: return launch_tile<BwdPowInt<0, false>>(L, st);

@@ -29,6 +29,9 @@ constexpr OpGeom geom_of() {
     return OpGeom{16 * Op::REG_N, Op::CTAS_PER_SM};
 }
 OpGeom fwd_pow_geom(FwdKind kind, int ip);
+OpGeom bwd_fused_geom(int iq);
+OpGeom bwd_x_geom(int iq);
+OpGeom bwd_w_geom(int iq);
 
 int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st);   // PowInt (ip 1..8), PowGen, PowNorm
 int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper}

@@ -92,7 +92,7 @@ __device__ __forceinline__ float2 ex2_mixed2(float2 e, int sel) {
     return ex2_fma2<DEG>(e);
 }
 constexpr int kMufuEveryFwd = 8;
-constexpr int kMufuEveryBwd = 4;
+constexpr int kMufuEveryBwd = 2;
 
 // |t|^IP by repeated multiplication, IP in 1..8
 template <int IP>
@@ -454,7 +454,7 @@ struct FwdBoundPos : FwdLayout {
 //   grad_w: out (m = o, n = c), k = (b, hw);  A = coefficient [k][m] (KMajor),  B = x [k][n] (KMajor),
 //           resident = w[m][n], t = B - resident, result negated
 // Integer p - 1: coefficient = g / y^(p-1), term = coefficient * sgn(t) |t|^(p-1).
-// General p:     coefficients r = 1 / y and g, term = g * sgn(t) * 2^((p-1) lg2(|t| r)).
+// General p:     coefficients c = -(p-1) lg2 y and g, term = g * sgn(t) * 2^((p-1) lg2|t| + c).
 // ------------------------------------------------------------------------------------------------
 template <bool WEIGHT>
 struct BwdLayout {
@@ -513,6 +513,10 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
     static constexpr bool PACKED = true;
+    // two CTAs of the 128 x 64 tile per SM (see BwdFusedGen)
+    static constexpr int STAGES = 2;
+    static constexpr int REG_N = 4;
+    static constexpr int CTAS_PER_SM = 2;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     template <int KS>
     __device__ static void update_pair(float& s0, float& s1, float p0, float p1, const float* r, const float* gr,
@@ -523,8 +527,8 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
         for (int k = 0; k < KS; ++k) {
             const float2 bb = make_float2(b0[k], b1[k]);
             const float2 t = WEIGHT ? pk_sub(bb, pr) : pk_sub(pr, bb);
-            const float2 l = make_float2(lg2_approx(fabsf(t.x) * r[k]), lg2_approx(fabsf(t.y) * r[k]));
-            const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__fmul2_rn(qq, l), sel + k);
+            const float2 l = make_float2(lg2_approx(fabsf(t.x)), lg2_approx(fabsf(t.y)));
+            const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__ffma2_rn(qq, l, make_float2(r[k], r[k])), sel + k);
             s0 = fmaf(gr[k], copysignf(v.x, t.x), s0);
             s1 = fmaf(gr[k], copysignf(v.y, t.y), s1);
         }
@@ -535,7 +539,7 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
             const float t = L::diff(pres, b[k]);
-            const float v = ex2_mixed<4>(P.q * lg2_approx(fabsf(t) * r[k]), sel + k);
+            const float v = ex2_mixed<4>(fmaf(P.q, lg2_approx(fabsf(t)), r[k]), sel + k);
             f[0] = fmaf(gr[k], copysignf(v, t), f[0]);
         }
     }
@@ -576,13 +580,16 @@ struct BwdFusedGen : BwdLayout<false> {
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
     static constexpr bool PACKED = true;
     static constexpr bool FUSED_W = true;
-    static constexpr int STAGES = 3;
+    // two CTAs of the 128 x 64 tile per SM: twice the warps to cover the MUFU / polynomial dependency chains
+    static constexpr int STAGES = 2;
+    static constexpr int REG_N = 4;
+    static constexpr int CTAS_PER_SM = 2;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     __device__ static float2 term_pair(float p0, float p1, float r, float gr, float b0, float b1, int sel,
                                        const TileParams& P, float2& coef) {
         const float2 t = pk_sub(make_float2(p0, p1), make_float2(b0, b1));
-        const float2 l = make_float2(lg2_approx(fabsf(t.x) * r), lg2_approx(fabsf(t.y) * r));
-        const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__fmul2_rn(make_float2(P.q, P.q), l), sel);
+        const float2 l = make_float2(lg2_approx(fabsf(t.x)), lg2_approx(fabsf(t.y)));
+        const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__ffma2_rn(make_float2(P.q, P.q), l, make_float2(r, r)), sel);
         coef = make_float2(gr, gr);
         return make_float2(copysignf(v.x, t.x), copysignf(v.y, t.y));
     }

@@ -108,13 +108,13 @@ __device__ __forceinline__ int thread_col(int tid) {
     return Op::FUSED_W ? (((tid >> 4) & 1) + 2 * (tid >> 5)) : (tid & 15);
 }
 
-constexpr int kSideBufferBytes = kTileK * kTileN * 4;  // column sums of one stage (fused backward)
 
 template <class Op>
 struct TileSmem {
     static constexpr int kTileN = 16 * Op::REG_N;
     static constexpr int kStage = Op::NUM_A * kOperandTileBytes + kTileN * kTileK * 4;
-    static constexpr int kSide = Op::FUSED_W ? 2 * kSideBufferBytes : 0;
+    static constexpr int kSideBuffer = kTileK * kTileN * 4;  // column sums of one stage (fused backward)
+    static constexpr int kSide = Op::FUSED_W ? 2 * kSideBuffer : 0;
     static constexpr int kTotal = Op::STAGES * kStage + kSide + 1024 /*alignment slack*/ + 64 /*barriers*/;
 };
 
@@ -131,7 +131,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     constexpr int RN = Op::REG_N;          // output columns per thread
     constexpr int TN = 16 * RN;            // output columns per tile
     constexpr int TELEMS = kTileM * TN;    // outputs per tile
-    static_assert(!Op::FUSED_W || RN == 8, "the fused backward uses the 128 x 128 tile");
+    static_assert(RN == 8 || RN == 4, "a thread owns 8 or 4 output columns");
 
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -196,15 +196,15 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         const long long tile_d = it_done / KT;
         const int kt_d = static_cast<int>(it_done - tile_d * KT);
         const TileCoord cd = tile_coord(P, tile_d, TN);
-        float* src = side + buf * (kTileK * kTileN);
+        float* src = side + buf * (kTileK * TN);
         float* dst_tile = P.side_out + (static_cast<size_t>(cd.m0 / kTileM) * P.G + cd.g) * (size_t)P.K * P.N;
         const bool vec = (P.N & 3) == 0;
 #pragma unroll
-        for (int q = 0; q < (kTileK * kTileN / 4) / kThreads; ++q) {
+        for (int q = 0; q < (kTileK * TN / 4) / kThreads; ++q) {
             const int idx4 = tid + kThreads * q;
-            const int r = idx4 >> 5;
-            const int c4 = (idx4 & 31) * 4;
-            float4* sp = reinterpret_cast<float4*>(src + r * kTileN + c4);
+            const int r = idx4 / (TN / 4);
+            const int c4 = (idx4 % (TN / 4)) * 4;
+            float4* sp = reinterpret_cast<float4*>(src + r * TN + c4);
             const float4 v = *sp;
             const int o = kt_d * kTileK + r;
             const int n = cd.n0 + c4;
@@ -291,7 +291,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 // and a column sum over the CTA's 128 rows (grad_weight of this row tile): summed over the
                 // thread's 8 rows in registers and over the warp's 16 row groups by shuffles; the finished
                 // column sums go to the stage's buffer with plain stores (every column has one owner).
-                float* buf = side + (ls & 1) * (kTileK * kTileN);
+                float* buf = side + (ls & 1) * (kTileK * TN);
 #pragma unroll
                 for (int k = 0; k < KS; ++k) {
                     float2 col[RN / 2];
@@ -314,24 +314,38 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                         }
                     // Sum over the 16 row groups of the warp (lane bits 0..3) with a halving butterfly:
                     // each exchange step passes on half of the values a lane still holds, so 8 values need
-                    // 4 + 2 + 1 shuffles plus one full step, and every lane ends with one finished column.
+                    // 4 + 2 + 1 shuffles plus one full step (4 values: 2 + 1 plus two full steps), and the
+                    // storing lanes end with one finished column each.
                     const bool b3 = (tid & 8) != 0, b2 = (tid & 4) != 0, b1 = (tid & 2) != 0;
-                    float v4[4], v2[2], v1;
-                    {
+                    if constexpr (RN == 8) {
+                        float v4[4], v2[2], v1;
+                        {
+                            const float c0 = col[0].x, c1 = col[0].y, c2 = col[1].x, c3 = col[1].y;
+                            const float c4 = col[2].x, c5 = col[2].y, c6 = col[3].x, c7 = col[3].y;
+                            v4[0] = (b3 ? c4 : c0) + __shfl_xor_sync(0xffffffffu, b3 ? c0 : c4, 8);
+                            v4[1] = (b3 ? c5 : c1) + __shfl_xor_sync(0xffffffffu, b3 ? c1 : c5, 8);
+                            v4[2] = (b3 ? c6 : c2) + __shfl_xor_sync(0xffffffffu, b3 ? c2 : c6, 8);
+                            v4[3] = (b3 ? c7 : c3) + __shfl_xor_sync(0xffffffffu, b3 ? c3 : c7, 8);
+                        }
+                        v2[0] = (b2 ? v4[2] : v4[0]) + __shfl_xor_sync(0xffffffffu, b2 ? v4[0] : v4[2], 4);
+                        v2[1] = (b2 ? v4[3] : v4[1]) + __shfl_xor_sync(0xffffffffu, b2 ? v4[1] : v4[3], 4);
+                        v1 = (b1 ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, b1 ? v2[0] : v2[1], 2);
+                        v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                        if ((tid & 1) == 0) {
+                            const int j = (b3 ? 4 : 0) + (b2 ? 2 : 0) + (b1 ? 1 : 0);
+                            buf[(ps * KS + k) * TN + own_index<Layout::KMajor, RN>(tn, j)] = v1;
+                        }
+                    } else {
                         const float c0 = col[0].x, c1 = col[0].y, c2 = col[1].x, c3 = col[1].y;
-                        const float c4 = col[2].x, c5 = col[2].y, c6 = col[3].x, c7 = col[3].y;
-                        v4[0] = (b3 ? c4 : c0) + __shfl_xor_sync(0xffffffffu, b3 ? c0 : c4, 8);
-                        v4[1] = (b3 ? c5 : c1) + __shfl_xor_sync(0xffffffffu, b3 ? c1 : c5, 8);
-                        v4[2] = (b3 ? c6 : c2) + __shfl_xor_sync(0xffffffffu, b3 ? c2 : c6, 8);
-                        v4[3] = (b3 ? c7 : c3) + __shfl_xor_sync(0xffffffffu, b3 ? c3 : c7, 8);
-                    }
-                    v2[0] = (b2 ? v4[2] : v4[0]) + __shfl_xor_sync(0xffffffffu, b2 ? v4[0] : v4[2], 4);
-                    v2[1] = (b2 ? v4[3] : v4[1]) + __shfl_xor_sync(0xffffffffu, b2 ? v4[1] : v4[3], 4);
-                    v1 = (b1 ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, b1 ? v2[0] : v2[1], 2);
-                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-                    if ((tid & 1) == 0) {
-                        const int j = (b3 ? 4 : 0) + (b2 ? 2 : 0) + (b1 ? 1 : 0);
-                        buf[(ps * KS + k) * kTileN + own_index<Layout::KMajor>(tn, j)] = v1;
+                        const float u0 = (b3 ? c2 : c0) + __shfl_xor_sync(0xffffffffu, b3 ? c0 : c2, 8);
+                        const float u1 = (b3 ? c3 : c1) + __shfl_xor_sync(0xffffffffu, b3 ? c1 : c3, 8);
+                        float v1 = (b2 ? u1 : u0) + __shfl_xor_sync(0xffffffffu, b2 ? u0 : u1, 4);
+                        v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+                        v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                        if ((tid & 3) == 0) {
+                            const int j = (b3 ? 2 : 0) + (b2 ? 1 : 0);
+                            buf[(ps * KS + k) * TN + own_index<Layout::KMajor, RN>(tn, j)] = v1;
+                        }
                     }
                 }
             } else if constexpr (Op::PACKED) {

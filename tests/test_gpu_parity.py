@@ -203,6 +203,32 @@ def test_finite_p_against_checker(C, shape, p):
     C.check_status()
 
 
+@pytest.mark.parametrize("shape", [(5, 20, 40, 1, 1), (3, 24, 70, 2, 3), (130, 36, 33, 1, 1)])
+@pytest.mark.parametrize("p", [60.0, 100.0])
+def test_general_p_backward_ragged_large_magnitudes(C, shape, p):
+    """Extents that are no multiples of the tile (rows of 128, reduction steps of 32) with |x - w| of 4..8: the
+    padding lanes of the general-p backward see |x - 0|^(p-1), which overflows fp32, and must still contribute
+    exactly nothing to either gradient."""
+    x, w, g = make_inputs(shape, 11)
+    x = (4.0 + 4.0 * x).astype(np.float32)
+    G = shape[3]
+    y = run_forward(C, x, w, p, G)
+    y_ref = oracle.norm_dist_forward(x, w, p, G)
+    assert rel(y.cpu().numpy(), y_ref) < rtol_for(p)
+    ogx, ogw = oracle.norm_dist_backward(g, x, w, y.cpu().numpy(), p, G)
+    tol = rtol_for(p, backward=True)
+    gx, gw = run_backward(C, g, x, w, y, p, G)
+    assert np.isfinite(gx.cpu().numpy()).all() and np.isfinite(gw.cpu().numpy()).all()
+    assert rel_to_max(gx.cpu().numpy(), ogx) < tol
+    assert rel_to_max(gw.cpu().numpy(), ogw) < tol
+    _, gw_only = run_backward(C, g, x, w, y, p, G, want_gx=False)
+    assert np.isfinite(gw_only.cpu().numpy()).all() and rel_to_max(gw_only.cpu().numpy(), ogw) < tol
+    gx_only = torch.full(x.shape, float("nan"), device="cuda")
+    C.norm_dist_backward_input(dev(g), dev(x), dev(w), y, gx_only, G, p)
+    assert rel_to_max(gx_only.cpu().numpy(), ogx) < tol
+    C.check_status()
+
+
 @pytest.mark.parametrize("shape", SHAPES)
 def test_inf_family_against_checker(C, shape):
     from l_inf_dist_net_v2_b200._lib import lib
