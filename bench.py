@@ -370,6 +370,9 @@ def run_ours(args, rank, world, local_rank):
 
     ffma_peak = probe(0, 4000)
     mufu_peak = probe(1, 1000)
+    # what the general-p instruction streams sustain on register operands (Tpair/s): fused backward, forward sum
+    mix_bwd_peak = probe(4, 500)
+    mix_fwd_peak = probe(5, 500)
     nominal_fp32 = sms * SM_LANES * max_mhz * 1e6 / 1e12
     nominal_mufu = sms * MUFU_LANES * max_mhz * 1e6 / 1e12
 
@@ -414,6 +417,11 @@ def run_ours(args, rank, world, local_rank):
                 if fam_ == "general" and name != "backward_fused":
                     mu = 2 * pairs / (t * 1e-3) / 1e12
                     row.update({"mufu_top_per_s": round(mu, 3), "frac_of_mufu_probe": round(mu / mufu_peak, 3)})
+                if fam_ == "general" and "tile_kernel_ms" in row:
+                    # the tile kernel against the register-only loop with the same per-pair instruction stream
+                    mix = mix_fwd_peak if name == "forward" else mix_bwd_peak
+                    row["tile_kernel_frac_of_mix_probe"] = round(
+                        pairs / (row["tile_kernel_ms"] * 1e-3) / 1e12 / mix, 3)
             rows.append(row)
         return rows
 
@@ -456,6 +464,8 @@ def run_ours(args, rank, world, local_rank):
             "traffic": None}
     line["kernels"] = rows
     line["probes"] = {"ffma_tlaneop_per_s": round(ffma_peak, 2), "mufu_top_per_s": round(mufu_peak, 3),
+                      "general_p_mix_bwd_tpair_per_s": round(mix_bwd_peak, 3),
+                      "general_p_mix_fwd_tpair_per_s": round(mix_fwd_peak, 3),
                       "nominal_fp32_tlaneop_per_s": round(nominal_fp32, 2),
                       "nominal_mufu_top_per_s": round(nominal_mufu, 3), "sms": sms}
     if world == 1 and not args.no_variants:

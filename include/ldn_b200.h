@@ -88,6 +88,9 @@ LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer);
  * *lane_ops then counts the MUFU operations only), `iters` iterations, on
  * 8 CTAs of 256 threads per SM.  *lane_ops receives the number of lane operations the launch executes
  * (FFMAs, respectively MUFU operations); the caller times the launch.  sink: one device float.
+ * kinds 4 and 5 run the per-pair instruction stream of the general-p kernels on register operands (4: the fused
+ * backward, 5: the sum pass of the forward; no shared memory, 4 CTAs per SM resident): *lane_ops then receives the
+ * number of (input, weight) pairs evaluated, so that pairs / time is the rate that instruction mix can sustain.
  */
 LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream);
 

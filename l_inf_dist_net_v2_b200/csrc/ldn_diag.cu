@@ -5,6 +5,7 @@
 
 #include "ldn_b200.h"
 #include "ldn_common.cuh"
+#include "ldn_ops.cuh"
 
 namespace ldn {
 std::atomic<unsigned long long> g_launches{0};
@@ -79,6 +80,46 @@ __global__ void __launch_bounds__(kProbeThreads) probe_kernel(int iters, float s
     for (int i = 0; i < kProbeIlp; ++i) s += v[i];
     if (s == 12345.678f) sink[0] = s;  // keeps the loop alive, practically never true
 }
+
+// kinds 4 / 5: the per-pair instruction stream of the general-p kernels on register operands only (no shared
+// memory, 8 independent packed chains per thread, 4 CTAs per SM): what the MUFU + FMA-pipe mix can sustain.
+// BWD: t = x - w, 2^(q lg2|t| + c) with every second exponential on MUFU, sign copy, two accumulations
+// (BwdFusedGen).  Forward: 2^(p lg2|t| + c) with one exponential in eight on MUFU, one accumulation
+// (FwdPowNorm).  Every chain step is two pairs.
+constexpr int kMixIlp = 8;
+template <bool BWD>
+__global__ void __launch_bounds__(kProbeThreads, 4) mix_probe_kernel(int iters, float q, float* sink) {
+    float2 x[kMixIlp], acc[kMixIlp], col[kMixIlp];
+    const float w0 = 0.3f + threadIdx.x * 1e-4f, off = -0.01f, g = 0.7f;
+#pragma unroll
+    for (int i = 0; i < kMixIlp; ++i) {
+        x[i] = make_float2(0.1f * i + threadIdx.x * 1e-3f, 0.2f * i + 0.05f);
+        acc[i] = make_float2(0.0f, 0.0f);
+        col[i] = make_float2(0.0f, 0.0f);
+    }
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < kMixIlp; ++i) {
+            x[i] = __fadd2_rn(x[i], make_float2(1e-4f, 1e-4f));  // keeps the chain from being hoisted
+            if (BWD) {
+                const float2 t = pk_sub(x[i], make_float2(w0, w0));
+                const float2 l = make_float2(lg2_approx(fabsf(t.x)), lg2_approx(fabsf(t.y)));
+                const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__ffma2_rn(make_float2(q, q), l, make_float2(off, off)), i);
+                const float2 sv = make_float2(copysignf(v.x, t.x), copysignf(v.y, t.y));
+                acc[i] = __ffma2_rn(sv, make_float2(g, g), acc[i]);
+                col[i] = __ffma2_rn(sv, make_float2(g, g), col[i]);
+            } else {
+                const float2 l = make_float2(lg2_approx(fabsf(x[i].x - w0)), lg2_approx(fabsf(x[i].y - w0)));
+                acc[i] = __fadd2_rn(acc[i], ex2_mixed2<3, kMufuEveryFwd>(
+                                                 __ffma2_rn(make_float2(q, q), l, make_float2(off, off)), i));
+            }
+        }
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMixIlp; ++i) s += acc[i].x + acc[i].y + col[i].x + col[i].y;
+    if (s == 12345.678f) sink[0] = s;
+}
 }  // namespace
 }  // namespace ldn
 
@@ -101,12 +142,19 @@ LDN_API float ldn_last_tile_kernel_ms(void) {
 LDN_API unsigned long long ldn_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream) {
-    if (!sink || !lane_ops || iters <= 0 || (kind < 0 || kind > 3)) return kBadArgument;
+    if (!sink || !lane_ops || iters <= 0 || (kind < 0 || kind > 5)) return kBadArgument;
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
     const int blocks = ctx->sm_count * 8;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (kind >= 4) {
+        if (kind == 4) mix_probe_kernel<true><<<blocks, kProbeThreads, 0, st>>>(iters, 36.5f, sink);
+        else mix_probe_kernel<false><<<blocks, kProbeThreads, 0, st>>>(iters, 37.5f, sink);
+        *lane_ops = static_cast<unsigned long long>(blocks) * kProbeThreads * iters * (2ull * kMixIlp);  // pairs
+        count_launches(1);
+        return cuda_status(cudaGetLastError());
+    }
     if (kind == 0) probe_kernel<0><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
     else if (kind == 2) probe_kernel<2><<<blocks, kProbeThreads, 0, st>>>(iters, 1.0f, sink);
     else if (kind == 3) probe_kernel<3><<<blocks, kProbeThreads, 0, st>>>(iters, 1.5f, sink);

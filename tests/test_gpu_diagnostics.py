@@ -36,7 +36,7 @@ def test_pipe_probes_report_plausible_rates(lib):
     sink = torch.zeros(64, device="cuda")
     ops = ctypes.c_ulonglong(0)
     rates = {}
-    for kind, iters in ((0, 2000), (1, 500), (2, 2000), (3, 500)):
+    for kind, iters in ((0, 2000), (1, 500), (2, 2000), (3, 500), (4, 300), (5, 300)):
         best = float("inf")
         for _ in range(3):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -51,6 +51,8 @@ def test_pipe_probes_report_plausible_rates(lib):
     assert 0.5 * nominal_fp32 < rates[0] < 1.1 * nominal_fp32
     assert 0.5 * nominal_fp32 < rates[2] < 1.1 * nominal_fp32
     assert 0.5 * nominal_fp32 / 8 < rates[1] < 1.1 * nominal_fp32 / 8
+    # general-p instruction streams: between 1 and 5 Tpair/s (1.5 / 1.125 MUFU operations per pair)
+    assert 1.0 < rates[4] < 5.0 and 1.0 < rates[5] < 5.0
     assert lib.ldn_probe_pipe(7, 10, sink.data_ptr(), ctypes.byref(ops), _stream()) == 1  # bad kind
 
 
