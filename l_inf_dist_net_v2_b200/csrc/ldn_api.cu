@@ -204,6 +204,10 @@ int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, c
     }
 }
 
+// The folded general-p backward evaluates 2^(q lg2|t| - q lg2 y): the absolute error of the logarithm (~2e-7) is
+// multiplied by q, so beyond this q the kernels take the logarithm of |t| / y (near 1 for the terms that matter).
+constexpr float kFoldMaxQ = 64.0f;
+
 // integer template value the reference dispatch would use for exponent e (norm_dist.cpp:17-35)
 int int_power(float e) {
     if (e == static_cast<float>(static_cast<int>(e)) && static_cast<int>(e) >= 0 && static_cast<int>(e) <= 8)
@@ -219,7 +223,9 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
     const int cap = cap_for(ctx);
-    const int iq = int_power(p - 1.0f);
+    int iq = int_power(p - 1.0f);
+    // general p: fold 1 / y into the exponent offset while q lg2|t| keeps the terms accurate to ~1e-5
+    if (iq < 0 && p - 1.0f > kFoldMaxQ) iq = -2;
     const int ncoef = iq >= 0 ? 1 : 2;
     // general p: coefficient arrays padded to whole tiles (see launch_coef_gen)
     const long long coef_rows = iq >= 0 ? s.M : (s.M + kTileM - 1) / kTileM * kTileM;
@@ -245,7 +251,7 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     const View cv0 = View{c0, coef_inner, coef_rows, s.G, coef_pitch, coef_rows * coef_pitch, 1};
     const View cv1 = View{c1 ? c1 : c0, coef_inner, coef_rows, s.G, coef_pitch, coef_rows * coef_pitch, 1};
     if (iq >= 0) r = launch_coef_int(go, y, c0, s, static_cast<int>(coef_pitch), iq, c.st);
-    else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(coef_pitch), coef_rows, p - 1.0f, c.st);
+    else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(coef_pitch), coef_rows, p - 1.0f, iq == -1, c.st);
     if (r != kOk) return r;
 
     if (fused) {

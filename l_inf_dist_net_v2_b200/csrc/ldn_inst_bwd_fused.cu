@@ -2,7 +2,7 @@
 #include "ldn_ops.cuh"
 
 namespace ldn {
-OpGeom bwd_fused_geom(int iq) { return iq >= 1 ? geom_of<BwdFusedInt<7>>() : geom_of<BwdFusedGen>(); }
+OpGeom bwd_fused_geom(int iq) { return iq >= 1 ? geom_of<BwdFusedInt<7>>() : geom_of<BwdFusedGen<true>>(); }
 
 int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st) {
     switch (iq) {
@@ -14,7 +14,8 @@ int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st) {
         case 6: return launch_tile<BwdFusedInt<6>>(L, st);
         case 7: return launch_tile<BwdFusedInt<7>>(L, st);
         case 8: return launch_tile<BwdFusedInt<8>>(L, st);
-        default: return launch_tile<BwdFusedGen>(L, st);
+        case -2: return launch_tile<BwdFusedGen<false>>(L, st);
+        default: return launch_tile<BwdFusedGen<true>>(L, st);
     }
 }
 }  // namespace ldn

@@ -2,7 +2,7 @@
 #include "ldn_ops.cuh"
 
 namespace ldn {
-OpGeom bwd_w_geom(int iq) { return iq >= 0 ? geom_of<BwdPowInt<7, true>>() : geom_of<BwdPowGen<true>>(); }
+OpGeom bwd_w_geom(int iq) { return iq >= 0 ? geom_of<BwdPowInt<7, true>>() : geom_of<BwdPowGen<true, true>>(); }
 
 int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st) {
     switch (iq) {
@@ -15,7 +15,8 @@ int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st) {
         case 6: return launch_tile<BwdPowInt<6, true>>(L, st);
         case 7: return launch_tile<BwdPowInt<7, true>>(L, st);
         case 8: return launch_tile<BwdPowInt<8, true>>(L, st);
-        default: return launch_tile<BwdPowGen<true>>(L, st);
+        case -2: return launch_tile<BwdPowGen<true, false>>(L, st);
+        default: return launch_tile<BwdPowGen<true, true>>(L, st);
     }
 }
 }  // namespace ldn

@@ -35,8 +35,9 @@ OpGeom bwd_w_geom(int iq);
 
 int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st);   // PowInt (ip 1..8), PowGen, PowNorm
 int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper}
-int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st);                   // iq 0..8, or -1 for general p
+// iq 0..8: integer p - 1; -1: general p with 1/y folded into the exponent offset; -2: general p, unfolded
+int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st);
 int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st);
-int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st);             // iq 1..8, or -1 for general p
+int launch_bwd_fused(int iq, const TileLaunch& L, cudaStream_t st);             // iq 1..8, -1 or -2
 
 }  // namespace ldn

@@ -508,7 +508,20 @@ struct BwdPowInt : BwdLayout<WEIGHT> {
     }
 };
 
-template <bool WEIGHT>
+// FOLD: coefficient 0 is the exponent offset c = -q lg2 y and the power is 2^(q lg2|t| + c); otherwise it is
+// 1 / y and the power is 2^(q lg2(|t| / y)) -- one multiply more per pair, but the logarithm is taken near 1 where
+// its absolute error is smallest, which matters once q reaches the hundreds.
+__device__ __forceinline__ float2 gen_exponent(float2 t, float c, float q, bool fold) {
+    if (fold) {
+        const float2 l = make_float2(lg2_approx(fabsf(t.x)), lg2_approx(fabsf(t.y)));
+        return __ffma2_rn(make_float2(q, q), l, make_float2(c, c));
+    }
+    const float2 u = __fmul2_rn(t, make_float2(c, c));
+    const float2 l = make_float2(lg2_approx(fabsf(u.x)), lg2_approx(fabsf(u.y)));
+    return __fmul2_rn(make_float2(q, q), l);
+}
+
+template <bool WEIGHT, bool FOLD>
 struct BwdPowGen : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
@@ -522,13 +535,11 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
     __device__ static void update_pair(float& s0, float& s1, float p0, float p1, const float* r, const float* gr,
                                        const float* b0, const float* b1, int sel, const TileParams& P) {
         const float2 pr = make_float2(p0, p1);
-        const float2 qq = make_float2(P.q, P.q);
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
             const float2 bb = make_float2(b0[k], b1[k]);
             const float2 t = WEIGHT ? pk_sub(bb, pr) : pk_sub(pr, bb);
-            const float2 l = make_float2(lg2_approx(fabsf(t.x)), lg2_approx(fabsf(t.y)));
-            const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__ffma2_rn(qq, l, make_float2(r[k], r[k])), sel + k);
+            const float2 v = ex2_mixed2<4, kMufuEveryBwd>(gen_exponent(t, r[k], P.q, FOLD), sel + k);
             s0 = fmaf(gr[k], copysignf(v.x, t.x), s0);
             s1 = fmaf(gr[k], copysignf(v.y, t.y), s1);
         }
@@ -539,7 +550,8 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
             const float t = L::diff(pres, b[k]);
-            const float v = ex2_mixed<4>(fmaf(P.q, lg2_approx(fabsf(t)), r[k]), sel + k);
+            const float v = ex2_mixed<4>(FOLD ? fmaf(P.q, lg2_approx(fabsf(t)), r[k]) : P.q * lg2_approx(fabsf(t) * r[k]),
+                                         sel + k);
             f[0] = fmaf(gr[k], copysignf(v, t), f[0]);
         }
     }
@@ -575,6 +587,7 @@ struct BwdFusedInt : BwdLayout<false> {
     }
 };
 
+template <bool FOLD>
 struct BwdFusedGen : BwdLayout<false> {
     using L = BwdLayout<false>;
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
@@ -588,8 +601,7 @@ struct BwdFusedGen : BwdLayout<false> {
     __device__ static float2 term_pair(float p0, float p1, float r, float gr, float b0, float b1, int sel,
                                        const TileParams& P, float2& coef) {
         const float2 t = pk_sub(make_float2(p0, p1), make_float2(b0, b1));
-        const float2 l = make_float2(lg2_approx(fabsf(t.x)), lg2_approx(fabsf(t.y)));
-        const float2 v = ex2_mixed2<4, kMufuEveryBwd>(__ffma2_rn(make_float2(P.q, P.q), l, make_float2(r, r)), sel);
+        const float2 v = ex2_mixed2<4, kMufuEveryBwd>(gen_exponent(t, r, P.q, FOLD), sel);
         coef = make_float2(gr, gr);
         return make_float2(copysignf(v.x, t.x), copysignf(v.y, t.y));
     }

@@ -125,26 +125,27 @@ __global__ void coef_int_flat_kernel(const float4* __restrict__ go, const float4
     }
 }
 __global__ void coef_gen_flat_kernel(const float4* __restrict__ go, const float4* __restrict__ y,
-                                     float4* __restrict__ rinv, float4* __restrict__ gcp, long long n4, float q) {
+                                     float4* __restrict__ rinv, float4* __restrict__ gcp, long long n4, float q, bool fold) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const float4 yv = y[i];
-        rinv[i] = make_float4(-q * log2f(yv.x), -q * log2f(yv.y), -q * log2f(yv.z), -q * log2f(yv.w));
+        rinv[i] = fold ? make_float4(-q * log2f(yv.x), -q * log2f(yv.y), -q * log2f(yv.z), -q * log2f(yv.w))
+                       : make_float4(1.0f / yv.x, 1.0f / yv.y, 1.0f / yv.z, 1.0f / yv.w);
         gcp[i] = go[i];
     }
 }
 
 // The general-p coefficient arrays are padded to whole tiles (rows to a multiple of 128, the inner extent to the
-// pitch, a multiple of 32): padding gets the offset -1e30, which sends 2^(q lg2|t| + offset) to (almost) zero
-// whatever |t| the zero-filled partner operand produces, and a zero gradient factor.
+// pitch, a multiple of 32): padding gets the offset -1e30 (folded form) or the factor 0 (1 / y form), which sends
+// the power to (almost) zero whatever |t| the zero-filled partner operand produces, and a zero gradient factor.
 __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ rinv,
-                                float* __restrict__ gcp, Shape s, int pitch, long long rows_pad, float q) {
+                                float* __restrict__ gcp, Shape s, int pitch, long long rows_pad, float q, bool fold) {
     const long long total = static_cast<long long>(s.G) * rows_pad * pitch;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const CanonIdx ci = canon_idx(i, pitch, rows_pad);
-        float off = -1e30f, gv = 0.0f;
+        float off = fold ? -1e30f : 0.0f, gv = 0.0f;
         if (ci.m < s.M && ci.c < s.COg) {
             const long long src = y_offset(s, ci);
-            off = -q * log2f(y[src]);
+            off = fold ? -q * log2f(y[src]) : 1.0f / y[src];
             gv = go[src];
         }
         rinv[i] = off;
@@ -318,17 +319,17 @@ int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s
     LDN_LAUNCH_RET();
 }
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
-                    long long rows_pad, float q, cudaStream_t st) {
+                    long long rows_pad, float q, bool fold, cudaStream_t st) {
     if (flat_ok(s, pitch, go, y) && rows_pad == s.M) {
         const long long n4 = static_cast<long long>(s.M) * s.COg / 4;
         coef_gen_flat_kernel<<<blocks_for(n4), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
                                                               reinterpret_cast<const float4*>(y),
                                                               reinterpret_cast<float4*>(rinv),
-                                                              reinterpret_cast<float4*>(gcp), n4, q);
+                                                              reinterpret_cast<float4*>(gcp), n4, q, fold);
         LDN_LAUNCH_RET();
     }
     coef_gen_kernel<<<blocks_for((long long)s.G * rows_pad * pitch), kBlock, 0, st>>>(go, y, rinv, gcp, s, pitch,
-                                                                                   rows_pad, q);
+                                                                                   rows_pad, q, fold);
     LDN_LAUNCH_RET();
 }
 

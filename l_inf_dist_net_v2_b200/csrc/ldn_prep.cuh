@@ -19,10 +19,11 @@ int launch_canon_bounds(const float* xl, const float* xu, float* lc, float* uc, 
 int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStream_t st);
 // integer p - 1 = iq:  coef[g][m][pitch] <- go / y^iq   (go, y in output layout)
 int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, cudaStream_t st);
-// general p: rinv[g][rows_pad][pitch] <- -q lg2 y (the exponent offset of (|t| / y)^q), gcp[g][rows_pad][pitch] <- go;
-// rows beyond M and columns beyond CO / G are padding (offset -1e30, gradient factor 0)
+// general p: rinv[g][rows_pad][pitch] <- -q lg2 y (fold: the exponent offset of (|t| / y)^q) or 1 / y,
+// gcp[g][rows_pad][pitch] <- go; rows beyond M and columns beyond CO / G are padding (offset -1e30 resp. factor 0,
+// gradient factor 0)
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
-                    long long rows_pad, float q,
+                    long long rows_pad, float q, bool fold,
                     cudaStream_t st);
 
 // Second step of the forward kernels that save an index: `pos` holds, per output, the id of the 32-channel
