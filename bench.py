@@ -428,8 +428,10 @@ def run_ours(args, rank, world, local_rank):
     # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
     # under profiles/; only valid for that shape and p
     ncu_traffic = {}
-    if (B, CI, CO, args.p) == (512, 3072, 5120, "8"):
-        ncu_traffic = {"forward": 76.8e6, "backward_fused": 405.0e6}
+    if (B, CI, CO) == (512, 3072, 5120):
+        ncu_traffic = {"8": {"forward": 76.8e6, "backward_fused": 405.0e6},
+                       "37.5": {"forward": 94.2e6, "backward_fused": 467.5e6},  # forward: the sum pass
+                       "inf": {"forward": 98.7e6}}.get(args.p, {})
     rows = kernel_rows(p, args.p, max(10, min(args.steps, 30)))
     in_step = [r for r in rows if r["kernel"] in (("forward", "grad_input", "grad_weight") if fam == "inf"
                                                  else ("forward", "backward_fused"))]

@@ -28,19 +28,26 @@ def allreduce_mean_(tensors, group=None, bucket_bytes=64 << 20):
     world = dist.get_world_size(group)
     if world == 1:
         return
+    # NCCL averages inside the collective; other backends (gloo) sum, then one division pass follows
+    avg = dist.get_backend(group) == "nccl"
     bucket, size = [], 0
+
+    def reduce_(t):
+        if avg:
+            dist.all_reduce(t, op=dist.ReduceOp.AVG, group=group)
+        else:
+            dist.all_reduce(t, group=group)
+            t.div_(world)
 
     def flush():
         nonlocal bucket, size
         if not bucket:
             return
         if len(bucket) == 1 and bucket[0].is_contiguous():
-            dist.all_reduce(bucket[0], group=group)
-            bucket[0].div_(world)
+            reduce_(bucket[0])
         else:
             flat = torch.cat([b.reshape(-1) for b in bucket])
-            dist.all_reduce(flat, group=group)
-            flat.div_(world)
+            reduce_(flat)
             off = 0
             for b in bucket:
                 b.copy_(flat[off:off + b.numel()].view_as(b))
