@@ -118,7 +118,9 @@ struct TileSmem {
     static constexpr int kTotal = Op::STAGES * kStage + kSide + 1024 /*alignment slack*/ + 64 /*barriers*/;
 };
 
-template <class Op>
+// RM = how many of a thread's 8 register rows are computed: 8, or 4 when the whole problem has at most 64 rows
+// (small batches) -- rows t + 16 r with r >= 4 are then all beyond M, in every tile and for every thread.
+template <class Op, int RM = kRegM>
 __global__ void __launch_bounds__(kThreads, Op::CTAS_PER_SM)
 tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
             const __grid_constant__ CUtensorMap map_b, const TileParams P) {
@@ -298,7 +300,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                     for (int jp = 0; jp < RN / 2; ++jp) col[jp] = make_float2(0.0f, 0.0f);
 #pragma unroll
-                    for (int i = 0; i < kRegM; ++i)
+                    for (int i = 0; i < RM; ++i)
 #pragma unroll
                         for (int jp = 0; jp < RN / 2; ++jp) {
                             // term = coef * base, folded into both accumulations as one FMA each
@@ -352,7 +354,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 // two neighbouring outputs (j, j + 1) at a time, so that the op can use the packed
                 // two-lane FP32 instructions (fma.rn.f32x2 ...): half the issue slots per lane operation
 #pragma unroll
-                for (int i = 0; i < kRegM; ++i)
+                for (int i = 0; i < RM; ++i)
 #pragma unroll
                     for (int j = 0; j < RN; j += 2)
                         Op::template update_pair<KS>(accf[i][j][0], accf[i][j + 1][0], pres[i][j], pres[i][j + 1],
@@ -360,7 +362,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                                                      i + (j >> 1), P);
             } else {
 #pragma unroll
-                for (int i = 0; i < kRegM; ++i)
+                for (int i = 0; i < RM; ++i)
 #pragma unroll
                     for (int j = 0; j < RN; ++j)
                         Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], sl.a0[i],
@@ -510,13 +512,22 @@ int launch_tile(const TileLaunch& L, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     constexpr int SMEM = TileSmem<Op>::kTotal;
+    // ops whose rows are batch rows also exist with half of the register rows, for problems of at most 64 rows
+    constexpr bool HALF = Op::LA == Layout::RowMajor;
     if (dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(tile_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess && HALF)
+            e = cudaFuncSetAttribute(tile_kernel<Op, (HALF ? kRegM / 2 : kRegM)>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return cuda_status(e);
         configured[dev] = true;
     }
     timing_before(stream);
-    tile_kernel<Op><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b, L.params);
+    if (HALF && L.params.M <= kTileM / 2)
+        tile_kernel<Op, (HALF ? kRegM / 2 : kRegM)><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b,
+                                                                                      L.params);
+    else
+        tile_kernel<Op><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b, L.params);
     timing_after(stream);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_status(e);
