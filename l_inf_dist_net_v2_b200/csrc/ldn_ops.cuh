@@ -189,6 +189,7 @@ struct FwdLayout {
     static constexpr bool PREFETCH = true;  // register double buffering of the operand slabs
     static constexpr bool FUSED_W = false;
     static constexpr bool STAGE_HOOK = false;  // op has a stage_end(f, n, stage) step after every 32-wide stage
+    static constexpr bool SHORT_STAGES = false;  // stop a partly filled last stage after its valid k-groups
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;        // output columns per thread: 8 (128 x 128 tile) or 4 (128 x 64)
     static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
@@ -230,6 +231,7 @@ struct FwdPowInt : FwdLayout {
 
 // sum of |t|^p = 2^(p lg2 |t|) for non-integer (or > 8) p <= 10
 struct FwdPowGen : FwdLayout {
+    static constexpr bool SHORT_STAGES = true;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
     static constexpr bool PACKED = true;
@@ -264,6 +266,7 @@ struct FwdPowGen : FwdLayout {
 // sum of (|t| / M)^p with a per-output normaliser M read from P.pres (layout of the output);
 // resident value = -p lg2 M.   y = M (sum + (1e-10 / M)^p)^(1/p)
 struct FwdPowNorm : FwdLayout {
+    static constexpr bool SHORT_STAGES = true;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = true;
     static constexpr bool PACKED = true;
@@ -311,6 +314,7 @@ struct FwdPowNorm : FwdLayout {
 // ------------------------------------------------------------------------------------------------
 template <bool POS>
 struct FwdInf : FwdLayout {
+    static constexpr bool SHORT_STAGES = !POS;
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
     static constexpr bool PREFETCH = false;  // two 4-wide slabs would not fit the register file
     // POS: f[0] = running maximum, f[1] = maximum inside the current 32-channel stage, n[0] = stage in which
@@ -369,6 +373,7 @@ struct FwdInf : FwdLayout {
 // (one per bound), each tracking the 4-channel group like FwdInf<true>.
 // ------------------------------------------------------------------------------------------------
 struct FwdBound : FwdLayout {
+    static constexpr bool SHORT_STAGES = true;
     static constexpr int NUM_A = 2, NF = 2, NI = 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) {
@@ -465,6 +470,7 @@ struct BwdLayout {
     static constexpr bool PREFETCH = false;  // the resident operand leaves no registers for it
     static constexpr bool FUSED_W = false;
     static constexpr bool STAGE_HOOK = false;
+    static constexpr bool SHORT_STAGES = false;
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;
     static constexpr int CTAS_PER_SM = 1;

@@ -369,21 +369,30 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                                                 NA == 2 ? sl.a1[i] : sl.a0[i], sl.b[j], chunk, i + j, P);
             }
         };
+        // Op::SHORT_STAGES: the last stage of a reduction that is no multiple of 32 (or a short one, K < 32) stops
+        // after its valid k-groups; an even count keeps the pairwise swap above and the double buffering below
+        // intact.  (The run-time trip count also changes how the compiler schedules the rolled loop: measured per
+        // op family at 512 x 3072 -> 5120, it is on where that was no slower.)
+        int nsteps = NSTEP;
+        if constexpr (Op::SHORT_STAGES) {
+            const int kvalid = P.K - kt * kTileK;
+            if (kvalid < kTileK) nsteps = (((kvalid + KS - 1) / KS) + 1) & ~1;
+        }
         if constexpr (Op::PREFETCH) {
             // register double buffering: the operands of the next k-group are read from shared memory
             // while the current group is computed (the loop is rolled, the compiler cannot do this itself)
             Slab s0, s1;
             load(s0, 0);
 #pragma unroll 1
-            for (int ks = 0; ks < NSTEP; ks += 2) {
+            for (int ks = 0; ks < nsteps; ks += 2) {
                 load(s1, ks + 1);
                 compute(s0, ks);
-                if (ks + 2 < NSTEP) load(s0, ks + 2);
+                if (ks + 2 < nsteps) load(s0, ks + 2);
                 compute(s1, ks + 1);
             }
         } else {
 #pragma unroll 1
-            for (int ks = 0; ks < NSTEP; ++ks) {
+            for (int ks = 0; ks < nsteps; ++ks) {
                 Slab sl;
                 load(sl, ks);
                 compute(sl, ks);
