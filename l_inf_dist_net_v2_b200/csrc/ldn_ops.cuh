@@ -190,6 +190,7 @@ struct FwdLayout {
     static constexpr bool FUSED_W = false;
     static constexpr bool STAGE_HOOK = false;  // op has a stage_end(f, n, stage) step after every 32-wide stage
     static constexpr bool SHORT_STAGES = false;  // stop a partly filled last stage after its valid k-groups
+    static constexpr int UNROLL = 1;             // unroll factor of the rolled k-group loop (measured per op)
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;        // output columns per thread: 8 (128 x 128 tile) or 4 (128 x 64)
     static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
@@ -202,6 +203,7 @@ struct FwdLayout {
 // sum of |t|^IP, then the p-th root with the underflow floor
 template <int IP>
 struct FwdPowInt : FwdLayout {
+    static constexpr int UNROLL = 2;
     static constexpr int KSTEP = 4;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
@@ -315,6 +317,7 @@ struct FwdPowNorm : FwdLayout {
 template <bool POS>
 struct FwdInf : FwdLayout {
     static constexpr bool SHORT_STAGES = !POS;
+    static constexpr int UNROLL = 4;
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
     static constexpr bool PREFETCH = false;  // two 4-wide slabs would not fit the register file
     // POS: f[0] = running maximum, f[1] = maximum inside the current 32-channel stage, n[0] = stage in which
@@ -471,6 +474,7 @@ struct BwdLayout {
     static constexpr bool FUSED_W = false;
     static constexpr bool STAGE_HOOK = false;
     static constexpr bool SHORT_STAGES = false;
+    static constexpr int UNROLL = 1;
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;
     static constexpr int CTAS_PER_SM = 1;
@@ -533,6 +537,7 @@ struct BwdPowGen : BwdLayout<WEIGHT> {
     static constexpr int NUM_A = 2, NF = 1, NI = 0;
     static constexpr bool PACKED = true;
     // two CTAs of the 128 x 64 tile per SM (see BwdFusedGen)
+    static constexpr int UNROLL = 4;
     static constexpr int STAGES = 2;
     static constexpr int REG_N = 4;
     static constexpr int CTAS_PER_SM = 2;
@@ -600,6 +605,7 @@ struct BwdFusedGen : BwdLayout<false> {
     static constexpr bool PACKED = true;
     static constexpr bool FUSED_W = true;
     // two CTAs of the 128 x 64 tile per SM: twice the warps to cover the MUFU / polynomial dependency chains
+    static constexpr int UNROLL = 2;
     static constexpr int STAGES = 2;
     static constexpr int REG_N = 4;
     static constexpr int CTAS_PER_SM = 2;

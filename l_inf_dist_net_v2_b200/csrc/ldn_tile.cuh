@@ -383,7 +383,8 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
             // while the current group is computed (the loop is rolled, the compiler cannot do this itself)
             Slab s0, s1;
             load(s0, 0);
-#pragma unroll 1
+            constexpr int UNR = Op::UNROLL;
+#pragma unroll UNR
             for (int ks = 0; ks < nsteps; ks += 2) {
                 load(s1, ks + 1);
                 compute(s0, ks);
@@ -391,7 +392,8 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 compute(s1, ks + 1);
             }
         } else {
-#pragma unroll 1
+            constexpr int UNR = Op::UNROLL;  // 1 = rolled; a few ops schedule better with two k-groups per trip
+#pragma unroll UNR
             for (int ks = 0; ks < nsteps; ++ks) {
                 Slab sl;
                 load(sl, ks);
