@@ -377,6 +377,9 @@ struct FwdInf : FwdLayout {
 // ------------------------------------------------------------------------------------------------
 struct FwdBound : FwdLayout {
     static constexpr bool SHORT_STAGES = true;
+    static constexpr int KSTEP = 4;  // measured best: 4-wide k-groups, no register double buffering, two per trip
+    static constexpr bool PREFETCH = false;
+    static constexpr int UNROLL = 2;
     static constexpr int NUM_A = 2, NF = 2, NI = 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) {
