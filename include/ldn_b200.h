@@ -61,6 +61,13 @@ LDN_API int ldn_release_scratch(void);
 LDN_API void ldn_set_max_ctas(int max_ctas);
 
 /*
+ * Scratch limit of the fused finite-p backward (bytes; 0 restores the default of 1 GiB).  The kernel keeps one
+ * copy of grad_weight per 128 rows of the batch; a batch that would need more than the limit is processed in
+ * chunks of whole samples whose weight gradients are added up.  No counterpart in the reference.
+ */
+LDN_API void ldn_set_fused_scratch_limit(unsigned long long bytes);
+
+/*
  * Number of kernels this library has launched in the calling process so far (all devices, all streams).
  * No counterpart in the reference.
  */

@@ -13,6 +13,8 @@ int release_arenas();
 namespace {
 
 int g_max_ctas = 0;
+// scratch the fused backward may use for its per-row-tile column sums (bytes); larger batches run in row chunks
+size_t g_side_limit = size_t(1) << 30;
 
 // A 3-D view of an operand for TMA: `inner` contiguous elements, `rows` rows, `groups` groups.
 // row_coord tells which tensor-map coordinate carries the row (1: dims are (inner, rows, groups);
@@ -215,10 +217,10 @@ int int_power(float e) {
     return -1;
 }
 
-int norm_dist_backward(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
-                       float* gw, float p, ldn_stream_t stream) {
-    if (!go || !x || !w || !y || (!gx && !gw)) return kBadArgument;
-    if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
+// One backward call on rows [0, s.B) of the given pointers.  accumulate_gw: add to grad_weight instead of
+// overwriting it (only the fused path supports that; it is how the row chunks of one call combine).
+int norm_dist_backward_part(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
+                            float* gw, float p, ldn_stream_t stream, bool accumulate_gw) {
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
@@ -236,7 +238,8 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     // tall problems (conv layouts with many rows) keep the two-kernel path; so does p = 1 (constant terms).
     const long long tiles_m = (s.M + kTileM - 1) / kTileM;
     const size_t side_floats = static_cast<size_t>(tiles_m) * s.CO * s.CIg;
-    const bool fused = gx && gw && iq != 0 && side_floats * sizeof(float) <= (size_t(1) << 30);
+    const bool fused = gx && gw && iq != 0 && side_floats * sizeof(float) <= g_side_limit;
+    if (accumulate_gw && !fused) return kBadArgument;
     size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + ncoef * pad256(coef_floats * sizeof(float)) +
                   2 * partial_bytes(cap, 1) + (fused ? pad256(side_floats * sizeof(float)) : 0);
     Call c;
@@ -273,7 +276,8 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
         if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
         if ((r = build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n)) != kOk) return r;
         if ((r = launch_bwd_fused(iq, L, c.st)) != kOk) return r;
-        return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m), c.st);
+        return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m),
+                                  accumulate_gw, c.st);
     }
     if (gx) {
         // out (m = (b, hw), n = c), k = o
@@ -312,6 +316,33 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
         if ((r = launch_bwd_w(iq, L, c.st)) != kOk) return r;
     }
     return kOk;
+}
+
+int norm_dist_backward(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
+                       float* gw, float p, ldn_stream_t stream) {
+    if (!go || !x || !w || !y || (!gx && !gw)) return kBadArgument;
+    if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
+    // The fused kernel keeps one copy of grad_weight per 128-row tile as scratch.  A batch whose copies would
+    // exceed the limit runs as chunks of whole samples, each within the limit; the chunks' weight gradients
+    // add up in grad_weight (stream order), their input gradients are disjoint row ranges.
+    if (gx && gw && int_power(p - 1.0f) != 0) {
+        const size_t tile_bytes = static_cast<size_t>(s.CO) * s.CIg * sizeof(float);
+        const long long max_tiles = static_cast<long long>(g_side_limit / tile_bytes);
+        const long long tiles_m = (s.M + kTileM - 1) / kTileM;
+        const long long chunk_b = max_tiles * kTileM / s.HW;
+        if (tiles_m > max_tiles && chunk_b >= 1) {
+            for (long long b0 = 0; b0 < s.B; b0 += chunk_b) {
+                Shape sc = s;
+                sc.B = static_cast<int>(s.B - b0 < chunk_b ? s.B - b0 : chunk_b);
+                sc.M = static_cast<long long>(sc.B) * s.HW;
+                const size_t oy = static_cast<size_t>(b0) * s.CO * s.HW, ox = static_cast<size_t>(b0) * s.CI * s.HW;
+                const int r = norm_dist_backward_part(go + oy, x + ox, w, y + oy, sc, gx + ox, gw, p, stream, b0 > 0);
+                if (r != kOk) return r;
+            }
+            return kOk;
+        }
+    }
+    return norm_dist_backward_part(go, x, w, y, s, gx, gw, p, stream, false);
 }
 
 int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* pos, ldn_stream_t stream) {
@@ -382,6 +413,10 @@ LDN_API const char* ldn_status_string(int status) {
 LDN_API const char* ldn_version(void) { return "ldn_b200 0.1 sm_100a"; }
 
 LDN_API void ldn_set_max_ctas(int max_ctas) { g_max_ctas = max_ctas > 0 ? max_ctas : 0; }
+
+LDN_API void ldn_set_fused_scratch_limit(unsigned long long bytes) {
+    g_side_limit = bytes > 0 ? static_cast<size_t>(bytes) : size_t(1) << 30;
+}
 
 LDN_API int ldn_release_scratch(void) { return release_arenas(); }
 

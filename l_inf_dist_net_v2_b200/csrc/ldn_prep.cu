@@ -210,11 +210,12 @@ __global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const
     }
 }
 
-__global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles) {
+__global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles,
+                                   bool accumulate) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
         float s = 0.0f;
         for (int t = 0; t < tiles; ++t) s += part[t * count + i];
-        gw[i] = -s;
+        gw[i] = accumulate ? gw[i] - s : -s;
     }
 }
 
@@ -340,8 +341,8 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
     LDN_LAUNCH_RET();
 }
 
-int launch_side_reduce(const float* part, float* gw, long long count, int tiles, cudaStream_t st) {
-    side_reduce_kernel<<<blocks_for(count), kBlock, 0, st>>>(part, gw, count, tiles);
+int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, cudaStream_t st) {
+    side_reduce_kernel<<<blocks_for(count), kBlock, 0, st>>>(part, gw, count, tiles, accumulate);
     LDN_LAUNCH_RET();
 }
 

@@ -36,7 +36,7 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
                   cudaStream_t st);
 
 // grad_weight of the fused backward: gw[i] = -sum_t part[t * count + i], t < tiles
-int launch_side_reduce(const float* part, float* gw, long long count, int tiles, cudaStream_t st);
+int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, cudaStream_t st);
 
 // p = inf backward: gx[b, idx] += v, gw[o, idx] -= v with v = pos >= 0 ? go : -go.  gx / gw may be null.
 int launch_inf_scatter(const float* go, const int* pos, float* gx, float* gw, const Shape& s, cudaStream_t st);

@@ -245,6 +245,37 @@ def test_large_exponent_gradients(C, p, tol):
     C.check_status()
 
 
+@pytest.mark.parametrize("shape", [(700, 96, 40, 1, 1), (300, 64, 48, 2, 1), (9, 24, 16, 1, 100)])
+@pytest.mark.parametrize("p", [8.0, 37.5])
+def test_fused_backward_in_row_chunks(C, shape, p):
+    """With the scratch limit of the fused backward lowered to two row tiles' worth, the batch is processed in
+    chunks of whole samples: the input gradient is written chunk by chunk, the weight gradient accumulates."""
+    from l_inf_dist_net_v2_b200._lib import lib
+    x, w, g = make_inputs(shape, 21)
+    B, CI, CO, G, HW = shape
+    y = run_forward(C, x, w, p, G)
+    ogx, ogw = oracle.norm_dist_backward(g, x, w, y.cpu().numpy(), p, G)
+    whole = run_backward(C, g, x, w, y, p, G)
+    lib.ldn_set_fused_scratch_limit(2 * CO * (CI // G) * 4)
+    try:
+        before = lib.ldn_kernel_launches()
+        chunked = run_backward(C, g, x, w, y, p, G)
+        launches = lib.ldn_kernel_launches() - before
+    finally:
+        lib.ldn_set_fused_scratch_limit(0)
+    rows_per_chunk = max(1, 2 * 128 // HW) * HW
+    assert launches >= 3 * -(-B * HW // rows_per_chunk)  # coefficients, tile kernel, column-sum reduction per chunk
+    tol = rtol_for(p, backward=True)
+    for got, ref_ in ((chunked[0], ogx), (chunked[1], ogw)):
+        assert rel_to_max(got.cpu().numpy(), ref_) < tol
+    # same terms, but the reduction over outputs may be split between CTAs at other places, and for general p a
+    # row's position inside its tile decides which of its exponentials take the polynomial (2.7e-6) path
+    same = 1e-6 if is_int_p(p - 1) else 2e-5
+    assert rel_to_max(chunked[0].cpu().numpy(), whole[0].cpu().numpy()) < same
+    assert rel_to_max(chunked[1].cpu().numpy(), whole[1].cpu().numpy()) < same
+    C.check_status()
+
+
 @pytest.mark.parametrize("shape", SHAPES)
 def test_inf_family_against_checker(C, shape):
     from l_inf_dist_net_v2_b200._lib import lib
