@@ -257,12 +257,10 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
     else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(coef_pitch), coef_rows, p - 1.0f, iq == -1, c.st);
     if (r != kOk) return r;
 
-    if (fused) {
-        float* side = c.bump.take<float>(side_floats);
-        if (!side) return kWorkspace;
-        TileLaunch L;
-        const OpGeom geom = bwd_fused_geom(iq);
-        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom)) != kOk) return r;
+    // grad_input-shaped problem (also the fused kernel's): out (m = (b, hw), n = c), k = o
+    auto plan_rows = [&](TileLaunch& L, const OpGeom geom) -> int {
+        int e = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom);
+        if (e != kOk) return e;
         TileParams& P = L.params;
         P.a_row_coord = cv0.row_coord;
         P.b_row_coord = wv.row_coord;
@@ -270,31 +268,24 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
         P.pres = as_operand(xv);
         P.out = x_addr(s);
         P.out_f0 = gx;
-        P.side_out = side;
         P.p = p; P.q = p - 1.0f;
-        if ((r = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n)) != kOk) return r;
+        if ((e = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return e;
+        if ((e = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return e;
+        return build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n);
+    };
+    if (fused) {
+        float* side = c.bump.take<float>(side_floats);
+        if (!side) return kWorkspace;
+        TileLaunch L;
+        if ((r = plan_rows(L, bwd_fused_geom(iq))) != kOk) return r;
+        L.params.side_out = side;
         if ((r = launch_bwd_fused(iq, L, c.st)) != kOk) return r;
         return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m),
                                   accumulate_gw, c.st);
     }
     if (gx) {
-        // out (m = (b, hw), n = c), k = o
         TileLaunch L;
-        const OpGeom geom = bwd_x_geom(iq);
-        if ((r = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom)) != kOk) return r;
-        TileParams& P = L.params;
-        P.a_row_coord = cv0.row_coord;
-        P.b_row_coord = wv.row_coord;
-        P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(wv);
-        P.pres = as_operand(xv);
-        P.out = x_addr(s);
-        P.out_f0 = gx;
-        P.p = p; P.q = p - 1.0f;
-        if ((r = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n)) != kOk) return r;
+        if ((r = plan_rows(L, bwd_x_geom(iq))) != kOk) return r;
         if ((r = launch_bwd_x(iq, L, c.st)) != kOk) return r;
     }
     if (gw) {
