@@ -191,6 +191,7 @@ struct FwdLayout {
     static constexpr bool STAGE_HOOK = false;  // op has a stage_end(f, n, stage) step after every 32-wide stage
     static constexpr bool SHORT_STAGES = false;  // stop a partly filled last stage after its valid k-groups
     static constexpr int UNROLL = 1;             // unroll factor of the rolled k-group loop (measured per op)
+    static constexpr bool N_IN_SMEM = false;     // integer accumulators live in shared memory, not registers
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;        // output columns per thread: 8 (128 x 128 tile) or 4 (128 x 64)
     static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
@@ -316,6 +317,7 @@ struct FwdPowNorm : FwdLayout {
 // ------------------------------------------------------------------------------------------------
 template <bool POS>
 struct FwdInf : FwdLayout {
+    static constexpr bool N_IN_SMEM = POS;  // frees 64 registers of the indexed kernel (0.83 -> 0.79 ms)
     static constexpr bool SHORT_STAGES = !POS;
     static constexpr int UNROLL = 4;
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
@@ -410,6 +412,10 @@ struct FwdBound : FwdLayout {
 
 template <bool UPPER>
 struct FwdBoundPos : FwdLayout {
+    static constexpr bool N_IN_SMEM = true;
+    static constexpr int STAGES = 3;  // 3 x 48 KB of operand tiles + 64 KB of stage ids
+    static constexpr int KSTEP = 4;
+    static constexpr int UNROLL = 2;
     static constexpr bool PREFETCH = false;
     // f[0] = running extremum, f[1] = extremum inside the current stage, n[0] = stage of the last strict
     // improvement (-1: never), as in FwdInf<true>
@@ -478,6 +484,7 @@ struct BwdLayout {
     static constexpr bool STAGE_HOOK = false;
     static constexpr bool SHORT_STAGES = false;
     static constexpr int UNROLL = 1;
+    static constexpr bool N_IN_SMEM = false;
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;
     static constexpr int CTAS_PER_SM = 1;

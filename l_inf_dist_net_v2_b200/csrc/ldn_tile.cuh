@@ -115,7 +115,9 @@ struct TileSmem {
     static constexpr int kStage = Op::NUM_A * kOperandTileBytes + kTileN * kTileK * 4;
     static constexpr int kSideBuffer = kTileK * kTileN * 4;  // column sums of one stage (fused backward)
     static constexpr int kSide = Op::FUSED_W ? 2 * kSideBuffer : 0;
-    static constexpr int kTotal = Op::STAGES * kStage + kSide + 1024 /*alignment slack*/ + 64 /*barriers*/;
+    // ops with N_IN_SMEM keep their integer accumulators (one per output, rarely written) in shared memory
+    static constexpr int kInts = Op::N_IN_SMEM ? kThreads * kRegM * Op::REG_N * Op::NI * 4 : 0;
+    static constexpr int kTotal = Op::STAGES * kStage + kSide + kInts + 1024 /*alignment slack*/ + 64 /*barriers*/;
 };
 
 // RM = how many of a thread's 8 register rows are computed: 8, or 4 when the whole problem has at most 64 rows
@@ -138,7 +140,8 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* side = reinterpret_cast<float*>(smem + STAGES * STAGE);  // two column-sum buffers (fused backward)
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE + TileSmem<Op>::kSide);
+    int* ints = reinterpret_cast<int*>(smem + STAGES * STAGE + TileSmem<Op>::kSide);  // N_IN_SMEM ops
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE + TileSmem<Op>::kSide + TileSmem<Op>::kInts);
 
     const int tid = threadIdx.x;
     const int tn = thread_col<Op>(tid);
@@ -225,7 +228,14 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     };
 
     float accf[kRegM][RN][NF];
-    int acci[kRegM][RN][NIA];
+    static_assert(!Op::N_IN_SMEM || NI == 1, "one integer accumulator per output in shared memory");
+    int acci[Op::N_IN_SMEM ? 1 : kRegM][Op::N_IN_SMEM ? 1 : RN][NIA];
+    // integer accumulators of output (i, j): registers, or this thread's slots of the shared array
+    // ([array][output][thread]: neighbouring threads touch neighbouring words)
+    auto iacc = [&](int i, int j) -> int* {
+        if constexpr (Op::N_IN_SMEM) return ints + (i * RN + j) * kThreads + tid;
+        else return acci[i][j];
+    };
     float pres[kRegM][RN];
     TileCoord tc = {0, 0, 0};
     long long seg_begin = it0;
@@ -242,7 +252,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
             for (int i = 0; i < kRegM; ++i)
 #pragma unroll
                 for (int j = 0; j < RN; ++j) {
-                    Op::init(accf[i][j], acci[i][j]);
+                    Op::init(accf[i][j], iacc(i, j));
                     if (Op::HAS_P) {
                         const int m = tc.m0 + own_index<Op::LA>(tm, i);
                         const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
@@ -365,7 +375,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 for (int i = 0; i < RM; ++i)
 #pragma unroll
                     for (int j = 0; j < RN; ++j)
-                        Op::template update<KS>(accf[i][j], acci[i][j], pres[i][j], sl.a0[i],
+                        Op::template update<KS>(accf[i][j], iacc(i, j), pres[i][j], sl.a0[i],
                                                 NA == 2 ? sl.a1[i] : sl.a0[i], sl.b[j], chunk, i + j, P);
             }
         };
@@ -405,7 +415,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < kRegM; ++i)
 #pragma unroll
-                for (int j = 0; j < RN; ++j) Op::stage_end(accf[i][j], acci[i][j], kt);
+                for (int j = 0; j < RN; ++j) Op::stage_end(accf[i][j], iacc(i, j), kt);
         }
 
         if (kt == KT - 1 || it == it1 - 1) {
@@ -417,7 +427,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                     for (int j = 0; j < RN; ++j) {
                         const int m = tc.m0 + own_index<Op::LA>(tm, i);
                         const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
-                        if (m < P.M && n < P.N) Op::finalize(accf[i][j], acci[i][j], pres[i][j], m, n, tc.g, P);
+                        if (m < P.M && n < P.N) Op::finalize(accf[i][j], iacc(i, j), pres[i][j], m, n, tc.g, P);
                     }
             } else {
                 const int slot = (tile == first_tile) ? 0 : 1;
@@ -431,7 +441,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                         for (int a = 0; a < NF; ++a) dst[a * TELEMS + e] = accf[i][j][a];
 #pragma unroll
-                        for (int a = 0; a < NI; ++a) dst[(NF + a) * TELEMS + e] = __int_as_float(acci[i][j][a]);
+                        for (int a = 0; a < NI; ++a) dst[(NF + a) * TELEMS + e] = __int_as_float(iacc(i, j)[a]);
                     }
             }
         }
