@@ -8,8 +8,8 @@
 // second kernel (`tile_fixup_kernel`) folds those partials in k order and finalises -- there is no
 // inter-CTA waiting anywhere.
 //
-// Operand tiles are fetched by TMA (cp.async.bulk.tensor, 3-D, no multicast) into a 4-stage
-// shared-memory ring, completion on one mbarrier per stage; out-of-range rows / k are zero-filled by
+// Operand tiles are fetched by TMA (cp.async.bulk.tensor, 3-D, no multicast) into a shared-memory ring of
+// Op::STAGES (2 to 4) stages, completion on one mbarrier per stage; out-of-range rows / k are zero-filled by
 // the TMA unit, and every op is written so that zero padding is neutral.  Two tile shapes exist:
 //   RowMajor: [128 rows][32 k]  (k contiguous in global memory), stored with the 128-byte swizzle;
 //   KMajor:   [32 k][128 cols]  (cols contiguous in global memory), stored linearly.
