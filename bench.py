@@ -451,10 +451,12 @@ def run_ours(args, rank, world, local_rank):
             "kernel_ms": dominant.get("tile_kernel_ms"), "call_ms": dominant["ms"],
             "call_frac": dominant["frac_of_ffma_probe"],
             "note": "achieved / frac use the tile kernel's own duration (CUDA events around that launch); call_* "
-                    "include the helper kernels of the same entry point",
+                    "include the helper kernels of the same entry point; general p: frac_of_instruction_mix_probe "
+                    "compares the kernel with a register-only loop of its MUFU + FMA instruction stream",
             "peak_source": "FFMA-loop probe measured in this run (MEASURED_PEAKS.json holds no FP32 figure)",
             "peak_nominal": round(nominal_fp32, 2), "frac_of_nominal": dominant["frac_of_nominal"],
             "slots_per_pair": dominant["slots_per_pair"], "ms": dominant["ms"],
+            "frac_of_instruction_mix_probe": dominant.get("tile_kernel_frac_of_mix_probe"),
             "traffic": ncu_traffic.get(dominant["kernel"]), "traffic_unit": "bytes per launch (ncu)",
             "algorithmic_bytes": (4 * (B * CO + B * CI + CO * CI) + 4 * (B * CI + CO * CI))
             if dominant["kernel"] == "backward_fused" else 4 * (B * CI + CO * CI + B * CO)}
