@@ -206,8 +206,9 @@ struct FwdLayout {
 // sum of |t|^IP, then the p-th root with the underflow floor
 template <int IP>
 struct FwdPowInt : FwdLayout {
-    static constexpr int UNROLL = 2;
+    static constexpr int UNROLL = 2;  // measured best: 4-wide k-groups, two per trip, no register double buffering
     static constexpr int KSTEP = 4;
+    static constexpr bool PREFETCH = false;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool HAS_P = false;
     static constexpr bool PACKED = true;
@@ -503,6 +504,8 @@ struct BwdLayout {
 template <int IQ, bool WEIGHT>
 struct BwdPowInt : BwdLayout<WEIGHT> {
     using L = BwdLayout<WEIGHT>;
+    static constexpr int KSTEP = 4;                 // measured best per gradient
+    static constexpr int UNROLL = WEIGHT ? 1 : 2;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool PACKED = IQ >= 1;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
@@ -597,6 +600,8 @@ struct BwdFusedInt : BwdLayout<false> {
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
     static constexpr bool PACKED = true;
     static constexpr bool FUSED_W = true;
+    static constexpr int KSTEP = 4;  // measured best: 4-wide k-groups, two per trip
+    static constexpr int UNROLL = 2;
     __device__ static void init(float* f, int*) { f[0] = 0.0f; }
     // term = coef * returned value
     __device__ static float2 term_pair(float p0, float p1, float c, float, float b0, float b1, int,
