@@ -3,6 +3,8 @@
 #include <math.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "ldn_b200.h"
 #include "ldn_launch.cuh"
 #include "ldn_prep.cuh"
@@ -88,6 +90,7 @@ struct Call {
     Bump bump;
     cudaStream_t st;
     int cap;  // persistent CTAs
+    std::unique_lock<std::mutex> lock;  // the arena's call mutex, released when the entry point returns
 };
 
 int begin_call(Call* c, ldn_stream_t stream, size_t scratch_bytes) {
@@ -97,6 +100,7 @@ int begin_call(Call* c, ldn_stream_t stream, size_t scratch_bytes) {
     c->cap = (g_max_ctas > 0 && g_max_ctas < c->ctx->sm_count) ? g_max_ctas : c->ctx->sm_count;
     r = get_arena(c->st, scratch_bytes, &c->arena);
     if (r != kOk) return r;
+    c->lock = std::unique_lock<std::mutex>(*static_cast<std::mutex*>(c->arena->call_mutex));
     c->bump = Bump{c->arena->base, 0, c->arena->capacity};
     return kOk;
 }
@@ -646,7 +650,7 @@ LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float*
     char* base = nullptr;
     if ((r = noalloc_scratch_address(&base)) != kOk) return r;
     Arena fixed{base + kNoAllocStatusBytes, kNoAllocScratchBytes - kNoAllocStatusBytes,
-                reinterpret_cast<int*>(base), nullptr};
+                reinterpret_cast<int*>(base), nullptr, nullptr};
     c.arena = &fixed;
     c.bump = Bump{fixed.base, 0, fixed.capacity};
     View xv, wv;

@@ -163,6 +163,8 @@ struct Arena {
     size_t capacity;
     int* status;   // device int, zeroed at creation
     int* status_host;  // pinned host mirror used when checking
+    void* call_mutex;  // std::mutex*: held for the length of one entry-point call, so that two host threads that
+                       // use the same stream cannot interleave launches that share the scratch block
 };
 int get_arena(cudaStream_t stream, size_t bytes, Arena** out);
 

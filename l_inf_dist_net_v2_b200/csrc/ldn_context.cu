@@ -55,14 +55,16 @@ int get_arena(cudaStream_t stream, size_t bytes, Arena** out) {
         ent = new ArenaEntry();
         ent->device = dev;
         ent->stream = stream;
-        ent->arena = Arena{nullptr, 0, nullptr, nullptr};
+        ent->arena = Arena{nullptr, 0, nullptr, nullptr, new std::mutex()};
         if (cudaMalloc(&ent->arena.status, 256) != cudaSuccess) {
+            delete static_cast<std::mutex*>(ent->arena.call_mutex);
             delete ent;
             return kWorkspace;
         }
         cudaMemset(ent->arena.status, 0, 256);
         if (cudaMallocHost(&ent->arena.status_host, sizeof(int)) != cudaSuccess) {
             cudaFree(ent->arena.status);
+            delete static_cast<std::mutex*>(ent->arena.call_mutex);
             delete ent;
             return kWorkspace;
         }
@@ -107,6 +109,7 @@ int release_arenas() {
         if (a->arena.base) cudaFree(a->arena.base);
         cudaFree(a->arena.status);
         cudaFreeHost(a->arena.status_host);
+        delete static_cast<std::mutex*>(a->arena.call_mutex);
         delete a;
     }
     g_arenas.swap(keep);

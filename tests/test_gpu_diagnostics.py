@@ -103,3 +103,42 @@ def test_kernel_timing_hook(lib):
     finally:
         lib.ldn_enable_kernel_timing(0)
     assert 0.0 < ms < 50.0
+
+
+def test_two_host_threads_on_one_stream(lib):
+    """Calls from two host threads that use the same stream share one scratch block; the library serialises such
+    calls, so each one's helper kernels and tile kernel stay together in stream order."""
+    import threading
+
+    import numpy as np
+    import oracle
+
+    rng = np.random.default_rng(7)
+    B, CI, CO, HW = 6, 30, 50, 3  # HW > 1 and CI % 4 != 0: both operands go through canonical copies in scratch
+    cases = []
+    for _ in range(2):
+        x = rng.random((B, CI, HW), dtype=np.float32)
+        w = rng.standard_normal((CO, CI)).astype(np.float32)
+        cases.append((torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.empty(B, CO, HW, device="cuda"),
+                      oracle.inf_dist_forward(x, w, 1)[0]))
+    stream = _stream()
+    errors = []
+
+    def worker(case):
+        xd, wd, yd, _ = case
+        for _ in range(200):
+            st = lib.ldn_inf_dist_forward_nograd(xd.data_ptr(), wd.data_ptr(), B, CO, CI, 1, HW, yd.data_ptr(), stream)
+            if st != 0:
+                errors.append(st)
+                return
+
+    threads = [threading.Thread(target=worker, args=(c,)) for c in cases]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    assert not errors
+    for _, _, yd, ref in cases:
+        assert np.array_equal(yd.cpu().numpy(), ref)
+    assert lib.ldn_check_status(stream) == 0
