@@ -89,6 +89,16 @@ LDN_API float ldn_last_tile_kernel_ms(void);
 LDN_API void ldn_set_trace_buffer(unsigned long long* device_buffer);
 
 /*
+ * Training-mode MeanShift of a fully connected layer in one kernel (the reference composes it from torch operators,
+ * core/modules/basic_modules.py:104-135): x and out are [B][C] row-major; mean[c] = sum_b x[b][c] / B;
+ * out = x - mean; if running_mean is not NULL, running_mean = running_mean * (1 - momentum) + momentum * mean;
+ * if mean_out is not NULL it receives the batch mean.  out may alias x.  With running_mean = NULL the same call is
+ * the backward pass (grad_in = grad_out - mean over the batch of grad_out).  Deterministic.
+ */
+LDN_API int ldn_mean_shift_rows(const float* x, int B, int C, float* running_mean, float momentum, float* out,
+                        float* mean_out, ldn_stream_t stream);
+
+/*
  * Pipe-throughput probe for roofline denominators (no counterpart in the reference).  kind 0 runs a loop
  * of independent FFMA chains, kind 2 the same chains issued as packed fma.rn.f32x2, kind 1 a loop of
  * independent ex2(lg2(x)) chains, kind 3 eight such MUFU chains beside eight packed-FMA chains (16 FMAs per step;

@@ -32,6 +32,7 @@ SIGNATURES = {
     "ldn_bound_inf_dist_backward_input_weight": [_c_float_p, _c_float_p, _c_int_p, _c_int_p] + [_i] * 5 +
                                                 [_c_float_p, _c_float_p, _c_float_p, _s],
     "ldn_inf_dist_forward_nograd_noalloc": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _s],
+    "ldn_mean_shift_rows": [_c_float_p, _i, _i, _c_float_p, _f, _c_float_p, _c_float_p, _s],
     "ldn_check_status": [_s],
     "ldn_release_scratch": [],
     "ldn_probe_pipe": [_i, _i, _c_float_p, ctypes.c_void_p, _s],

@@ -9,6 +9,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import norm_dist_cuda as _C
 from .norm_dist import norm_dist, bound_inf_dist
 
 __all__ = ["NormDistBase", "NormDist", "NormDistConv", "MeanShift", "apply_if_not_none"]
@@ -16,6 +17,24 @@ __all__ = ["NormDistBase", "NormDist", "NormDistConv", "MeanShift", "apply_if_no
 
 def apply_if_not_none(paras, func):
     return [None if x is None else func(x) for x in paras]
+
+
+class _MeanShiftRowsF(torch.autograd.Function):
+    """x - (mean of x over the batch) for (B, C, 1) inputs, with the running-mean update, as one kernel per pass.
+    d(out)/d(x) = I - (1/B) 1 1^T, so the backward pass is the same kernel on the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, x, running_mean, momentum):
+        out = torch.empty_like(x)
+        _C.mean_shift_rows(x, running_mean, momentum, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        grad_output = grad_output.contiguous()
+        grad_input = torch.empty_like(grad_output)
+        _C.mean_shift_rows(grad_output, None, 0.0, grad_input)
+        return grad_input, None, None
 
 
 class MeanShift(nn.Module):
@@ -27,6 +46,7 @@ class MeanShift(nn.Module):
         self.out_channels = out_channels
         self.momentum = momentum
         self.affine = affine
+        self.fused = True  # use the one-kernel path where it applies (set False for the torch operators)
         self.register_buffer("running_mean", torch.zeros(out_channels))
         if affine:
             self.bias = nn.Parameter(torch.zeros(out_channels))
@@ -40,6 +60,10 @@ class MeanShift(nn.Module):
     def forward(self, x=None, lower=None, upper=None):
         if self.training:
             assert x is not None, "Currently not supported"
+            if (lower is None and upper is None and self.bias is None and x.is_cuda and x.dtype == torch.float32
+                    and x.dim() == 3 and x.size(2) == 1 and x.is_contiguous() and self.fused):
+                # fully connected layer: mean, running-mean update and subtraction in one kernel
+                return _MeanShiftRowsF.apply(x, self.running_mean, self.momentum), None, None
             mean = x.mean(dim=[0, 2])
             with torch.no_grad():
                 self.running_mean.mul_(1 - self.momentum).add_(mean, alpha=self.momentum)

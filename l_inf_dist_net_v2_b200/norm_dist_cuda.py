@@ -151,6 +151,16 @@ def bound_inf_dist_backward_input_weight(grad_outputL, grad_outputU, posL, posU,
               "bound_inf_dist_backward_input_weight")
 
 
+def mean_shift_rows(x, running_mean, momentum, out):
+    """Not part of the reference's extension module: out = x - mean over dim 0 of the (B, C) view of x, and, when
+    running_mean is given, running_mean <- (1 - momentum) running_mean + momentum mean, in one kernel."""
+    a, y = _f(x, "x"), _f(out, "out")
+    rm = None if running_mean is None else _f(running_mean, "running_mean")
+    B, C = x.size(0), x.numel() // max(x.size(0), 1)
+    with torch.cuda.device(x.device):
+        check(lib.ldn_mean_shift_rows(a, B, C, rm, float(momentum), y, None, _stream()), "mean_shift_rows")
+
+
 def check_status():
     """Waits for the current stream and raises if a kernel reported a bounded-wait timeout."""
     check(lib.ldn_check_status(_stream()), "device status check")

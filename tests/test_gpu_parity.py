@@ -581,3 +581,34 @@ def test_empty_batch_is_a_no_op(C):
     C.inf_dist_backward_input_weight(y, pos, torch.empty_like(x), gw, 1)
     assert torch.all(gw == 0)
     C.check_status()
+
+
+def test_fused_mean_shift_matches_torch_operators(C):
+    """The one-kernel training-mode MeanShift of fully connected layers against the torch operators the reference
+    composes it from (core/modules/basic_modules.py:104-135): output, running mean and input gradient."""
+    import l_inf_dist_net_v2_b200 as ldn
+    torch.manual_seed(3)
+    for B, Cn in ((512, 5120), (37, 70), (1, 5)):
+        fused = ldn.MeanShift(Cn, affine=False).cuda().train()
+        plain = ldn.MeanShift(Cn, affine=False).cuda().train()
+        plain.fused = False
+        start = torch.randn(Cn, device="cuda")
+        fused.running_mean.copy_(start)
+        plain.running_mean.copy_(start)
+        x1 = (torch.randn(B, Cn, 1, device="cuda") * 3 + 1).requires_grad_(True)
+        x2 = x1.detach().clone().requires_grad_(True)
+        g = torch.randn(B, Cn, 1, device="cuda")
+        y1 = fused(x1)[0]
+        y2 = plain(x2)[0]
+        y1.backward(g)
+        y2.backward(g)
+        assert torch.allclose(y1, y2, rtol=0, atol=2e-6 * 4)
+        assert torch.allclose(fused.running_mean, plain.running_mean, rtol=1e-6, atol=1e-6)
+        assert torch.allclose(x1.grad, x2.grad, rtol=0, atol=1e-6)
+        # eval mode and the bound triple keep the torch path
+        fused.eval()
+        plain.eval()
+        lo, up = x1.detach() - 0.1, x1.detach() + 0.1
+        for a, b in zip(fused(x1.detach(), lo, up), plain(x2.detach(), lo, up)):
+            assert torch.allclose(a, b, rtol=0, atol=1e-6)
+    C.check_status()
