@@ -7,4 +7,9 @@ from . import norm_dist_cuda  # noqa: F401  (loads the native library)
 from .norm_dist import norm_dist, bound_inf_dist, NormDistF, BoundInfDistF  # noqa: F401
 from .modules import NormDistBase, NormDist, NormDistConv, MeanShift, apply_if_not_none  # noqa: F401
 
-__version__ = "0.1"
+from .bound_modules import BoundSequential, BoundTanh, BoundReLU, BoundLinear, BoundFinalLinear  # noqa: F401
+from .models import MLPModel, HybridModel, check_inf_and_eval, set_p_norm  # noqa: F401
+from .attack import AttackPGD  # noqa: F401
+from . import losses  # noqa: F401
+
+__version__ = "0.2"
