@@ -19,7 +19,8 @@
  * successful no-op: nothing is launched, a weight gradient is set to zero.
  *
  * Scratch: kernels that need intermediate device memory take it from a per-(device, stream) arena that
- * the library allocates on first use and grows on demand (cudaMalloc; a growth synchronises the stream).
+ * the library allocates on first use and grows on demand (cudaMalloc; a growth synchronises the stream and is
+ * refused with status 6 while the stream is being captured, see ldn_reserve_scratch).
  * Calls issued on the same stream may follow each other freely; the same stream must not be used from
  * two host threads at once.
  */
@@ -51,8 +52,20 @@ LDN_API const char* ldn_version(void);
  */
 LDN_API int ldn_check_status(ldn_stream_t stream);
 
-/* Releases every scratch arena of the current device (synchronises the device). */
+/*
+ * Releases every scratch arena of the current device (synchronises the device).  CUDA graphs that captured calls of
+ * this library on the device refer to the released blocks: do not replay them afterwards.
+ */
 LDN_API int ldn_release_scratch(void);
+
+/*
+ * Makes the scratch arena of (current device, stream) at least `bytes` large now, so that later calls on the stream
+ * find it large enough (no counterpart in the reference).  Scratch cannot grow while the stream is being captured
+ * into a CUDA graph -- a call that would need to returns status 6 -- so before a capture either run the same calls
+ * once eagerly or reserve here.  Once a capture has used an arena, a later growth keeps the earlier blocks until
+ * ldn_release_scratch, so graphs captured before stay valid.
+ */
+LDN_API int ldn_reserve_scratch(ldn_stream_t stream, unsigned long long bytes);
 
 /*
  * Test hook: cap the number of persistent CTAs of the tile kernels (0 = one per SM).  Lets tests force
@@ -223,11 +236,19 @@ LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, 
  *     has to start at zero (every word is written before it is read within a call), but two calls whose
  *     kernels overlap on the GPU -- different streams, or different host threads -- race on it: issue these
  *     calls on one stream, or order them with events.
- *   - A bounded-wait timeout inside a kernel is recorded in the first word of the array; ldn_check_status
- *     does not report it.
+ *   - A bounded-wait timeout inside a kernel is recorded in the first word of the array, not in the stream's
+ *     arena: read it with ldn_noalloc_check_status (ldn_check_status does not see it).
  */
 LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float* weight, int B, int CO, int CI,
                                                 int G, int HW, float* output, ldn_stream_t stream);
+
+/*
+ * Status of the allocation-free entry point on the current device (no counterpart in the reference): copies the
+ * status word of the fixed array to the host in stream order, clears it, waits for the stream and returns it --
+ * 0 when every allocation-free call issued on this stream so far ran to completion, 4 when a bounded wait inside
+ * one of their kernels gave up (its output is then incomplete).  Allocates nothing either.
+ */
+LDN_API int ldn_noalloc_check_status(ldn_stream_t stream);
 
 #ifdef __cplusplus
 }

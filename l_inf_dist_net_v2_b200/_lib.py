@@ -34,7 +34,9 @@ SIGNATURES = {
     "ldn_inf_dist_forward_nograd_noalloc": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _s],
     "ldn_mean_shift_rows": [_c_float_p, _i, _i, _c_float_p, _f, _c_float_p, _c_float_p, _s],
     "ldn_check_status": [_s],
+    "ldn_noalloc_check_status": [_s],
     "ldn_release_scratch": [],
+    "ldn_reserve_scratch": [_s, ctypes.c_ulonglong],
     "ldn_probe_pipe": [_i, _i, _c_float_p, ctypes.c_void_p, _s],
 }
 OTHER_SYMBOLS = ["ldn_status_string", "ldn_version", "ldn_set_max_ctas", "ldn_kernel_launches", "ldn_set_trace_buffer",

@@ -98,9 +98,10 @@ int begin_call(Call* c, ldn_stream_t stream, size_t scratch_bytes) {
     if (r != kOk) return r;
     c->st = reinterpret_cast<cudaStream_t>(stream);
     c->cap = (g_max_ctas > 0 && g_max_ctas < c->ctx->sm_count) ? g_max_ctas : c->ctx->sm_count;
-    r = get_arena(c->st, scratch_bytes, &c->arena);
+    r = find_arena(c->st, &c->arena);
     if (r != kOk) return r;
     c->lock = std::unique_lock<std::mutex>(*static_cast<std::mutex*>(c->arena->call_mutex));
+    if ((r = ensure_arena(c->arena, c->st, scratch_bytes)) != kOk) return r;
     c->bump = Bump{c->arena->base, 0, c->arena->capacity};
     return kOk;
 }
@@ -399,6 +400,9 @@ LDN_API const char* ldn_status_string(int status) {
         case kWorkspace: return "scratch memory could not be provided";
         case kDeviceTimeout: return "a bounded wait inside a kernel gave up";
         case kTensorMap: return "the driver rejected a TMA descriptor";
+        case kCaptureGrowth:
+            return "the scratch arena would have to grow while its stream is being captured: issue the same call once "
+                   "before the capture, or reserve the scratch with ldn_reserve_scratch";
         default: break;
     }
     if (status >= kCudaBase) return cudaGetErrorString(static_cast<cudaError_t>(status - kCudaBase));
@@ -415,10 +419,19 @@ LDN_API void ldn_set_fused_scratch_limit(unsigned long long bytes) {
 
 LDN_API int ldn_release_scratch(void) { return release_arenas(); }
 
+LDN_API int ldn_reserve_scratch(ldn_stream_t stream, unsigned long long bytes) {
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    Arena* arena;
+    int r = find_arena(st, &arena);
+    if (r != kOk) return r;
+    std::lock_guard<std::mutex> lock(*static_cast<std::mutex*>(arena->call_mutex));
+    return ensure_arena(arena, st, static_cast<size_t>(bytes));
+}
+
 LDN_API int ldn_check_status(ldn_stream_t stream) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     Arena* arena;
-    int r = get_arena(st, 0, &arena);
+    int r = find_arena(st, &arena);
     if (r != kOk) return r;
     cudaError_t e = cudaMemcpyAsync(arena->status_host, arena->status, sizeof(int), cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaMemsetAsync(arena->status, 0, sizeof(int), st);
@@ -611,10 +624,12 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratch
 // In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address; the address a
 // kernel may use comes from cudaGetSymbolAddress, looked up once per device with that device current.
 char* g_noalloc_ptr[64] = {};
+std::mutex g_noalloc_mutex;
 
 int noalloc_scratch_address(char** out) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kNoDevice;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
     if (!g_noalloc_ptr[dev]) {
         void* p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
@@ -650,13 +665,27 @@ LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float*
     char* base = nullptr;
     if ((r = noalloc_scratch_address(&base)) != kOk) return r;
     Arena fixed{base + kNoAllocStatusBytes, kNoAllocScratchBytes - kNoAllocStatusBytes,
-                reinterpret_cast<int*>(base), nullptr, nullptr};
+                reinterpret_cast<int*>(base), nullptr, nullptr, false, nullptr};
     c.arena = &fixed;
     c.bump = Bump{fixed.base, 0, fixed.capacity};
     View xv, wv;
     if ((r = get_x_view(c, input, s, &xv)) != kOk) return r;
     if ((r = get_w_view(c, weight, s, &wv)) != kOk) return r;
     return run_forward(c, FwdKind::Inf, 0, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, INFINITY);
+}
+
+LDN_API int ldn_noalloc_check_status(ldn_stream_t stream) {
+    char* base = nullptr;
+    int r = noalloc_scratch_address(&base);
+    if (r != kOk) return r;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // a plain host int: the runtime stages the copy itself, nothing is allocated on the device
+    int word = 0;
+    cudaError_t e = cudaMemcpyAsync(&word, base, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(base, 0, sizeof(int), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_status(e);
+    return word;
 }
 
 }  // extern "C"

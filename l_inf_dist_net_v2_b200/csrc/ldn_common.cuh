@@ -18,6 +18,7 @@ enum Status : int {
     kWorkspace = 3,        // workspace allocation failed or fixed scratch too small
     kDeviceTimeout = 4,    // a bounded wait inside a kernel gave up (status word set by the device)
     kTensorMap = 5,        // cuTensorMapEncodeTiled rejected a descriptor
+    kCaptureGrowth = 6,    // the scratch arena would have to grow while its stream is being captured
     kCudaBase = 1000
 };
 
@@ -155,9 +156,8 @@ struct DeviceCtx {
 // Cached per-device properties for the current device; nullptr + status on failure.
 int get_device_ctx(const DeviceCtx** out);
 
-// Per-(device, stream) scratch arena owned by the library.  `bytes` is the total for the call;
-// the arena grows monotonically.  The region is 256-byte aligned.  The arena also carries the device
-// status word.
+// Per-(device, stream) scratch arena owned by the library.  The block grows on demand (never while the stream is
+// being captured) and is 256-byte aligned.  The arena also carries the device status word.
 struct Arena {
     char* base;
     size_t capacity;
@@ -165,8 +165,11 @@ struct Arena {
     int* status_host;  // pinned host mirror used when checking
     void* call_mutex;  // std::mutex*: held for the length of one entry-point call, so that two host threads that
                        // use the same stream cannot interleave launches that share the scratch block
+    bool graph_used;   // a call was issued on this arena while its stream was being captured
+    void* retired;     // std::vector<void*>*: earlier blocks that captured graphs may still refer to
 };
-int get_arena(cudaStream_t stream, size_t bytes, Arena** out);
+int find_arena(cudaStream_t stream, Arena** out);
+int ensure_arena(Arena* arena, cudaStream_t stream, size_t bytes);  // caller holds call_mutex
 
 // Bump allocator over an arena (256-byte granularity).
 struct Bump {

@@ -44,7 +44,8 @@ int get_device_ctx(const DeviceCtx** out) {
     return kOk;
 }
 
-int get_arena(cudaStream_t stream, size_t bytes, Arena** out) {
+// Finds (or creates, with its status word) the arena of (current device, stream).  Never touches the scratch block.
+int find_arena(cudaStream_t stream, Arena** out) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess) return kNoDevice;
     std::lock_guard<std::mutex> lock(g_mutex);
@@ -55,43 +56,67 @@ int get_arena(cudaStream_t stream, size_t bytes, Arena** out) {
         ent = new ArenaEntry();
         ent->device = dev;
         ent->stream = stream;
-        ent->arena = Arena{nullptr, 0, nullptr, nullptr, new std::mutex()};
-        if (cudaMalloc(&ent->arena.status, 256) != cudaSuccess) {
+        ent->arena = Arena{nullptr, 0, nullptr, nullptr, new std::mutex(), false, new std::vector<void*>()};
+        auto drop = [&]() {
             delete static_cast<std::mutex*>(ent->arena.call_mutex);
+            delete static_cast<std::vector<void*>*>(ent->arena.retired);
             delete ent;
+        };
+        if (cudaMalloc(&ent->arena.status, 256) != cudaSuccess) {
+            drop();
             return kWorkspace;
         }
         cudaMemset(ent->arena.status, 0, 256);
         if (cudaMallocHost(&ent->arena.status_host, sizeof(int)) != cudaSuccess) {
             cudaFree(ent->arena.status);
-            delete static_cast<std::mutex*>(ent->arena.call_mutex);
-            delete ent;
+            drop();
             return kWorkspace;
         }
         *ent->arena.status_host = 0;
         g_arenas.push_back(ent);
     }
-    if (bytes > ent->arena.capacity) {
-        // kernels already queued on the stream may still use the old block
-        cudaStreamSynchronize(stream);
-        if (ent->arena.base) cudaFree(ent->arena.base);
-        ent->arena.base = nullptr;
-        ent->arena.capacity = 0;
-        size_t want = bytes + bytes / 8;
-        want = (want + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-        void* p = nullptr;
-        if (cudaMalloc(&p, want) != cudaSuccess) {
-            cudaGetLastError();
-            if (cudaMalloc(&p, bytes) != cudaSuccess) {
-                cudaGetLastError();
-                return kWorkspace;
-            }
-            want = bytes;
-        }
-        ent->arena.base = static_cast<char*>(p);
-        ent->arena.capacity = want;
-    }
     *out = &ent->arena;
+    return kOk;
+}
+
+// Makes the arena's block at least `bytes` large.  The caller holds the arena's call mutex, so no other host thread
+// is enqueueing kernels that use the block.  While the stream is being captured nothing may be allocated or waited
+// for, so a growth is refused then; and once a capture has used the arena, earlier blocks are kept (a captured
+// graph replays with the addresses it was recorded with) until ldn_release_scratch.
+int ensure_arena(Arena* arena, cudaStream_t stream, size_t bytes) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        cs = cudaStreamCaptureStatusNone;
+    }
+    const bool capturing = cs != cudaStreamCaptureStatusNone;
+    if (capturing) arena->graph_used = true;
+    if (bytes <= arena->capacity) return kOk;
+    if (capturing) return kCaptureGrowth;
+    // kernels already queued on the stream may still use the old block
+    cudaStreamSynchronize(stream);
+    if (arena->base) {
+        if (arena->graph_used) static_cast<std::vector<void*>*>(arena->retired)->push_back(arena->base);
+        else cudaFree(arena->base);
+    }
+    arena->base = nullptr;
+    const size_t old_cap = arena->capacity;
+    arena->capacity = 0;
+    size_t want = bytes + bytes / 8;
+    // kept blocks add up: grow geometrically then, so that they stay below twice the final size
+    if (arena->graph_used && want < old_cap + old_cap / 2) want = old_cap + old_cap / 2;
+    want = (want + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    void* p = nullptr;
+    if (cudaMalloc(&p, want) != cudaSuccess) {
+        cudaGetLastError();
+        if (cudaMalloc(&p, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return kWorkspace;
+        }
+        want = bytes;
+    }
+    arena->base = static_cast<char*>(p);
+    arena->capacity = want;
     return kOk;
 }
 
@@ -107,6 +132,9 @@ int release_arenas() {
             continue;
         }
         if (a->arena.base) cudaFree(a->arena.base);
+        auto* retired = static_cast<std::vector<void*>*>(a->arena.retired);
+        for (void* p : *retired) cudaFree(p);
+        delete retired;
         cudaFree(a->arena.status);
         cudaFreeHost(a->arena.status_host);
         delete static_cast<std::mutex*>(a->arena.call_mutex);

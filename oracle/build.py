@@ -12,7 +12,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "_build", "libldn_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libldn_ref.so")
-REF_ROOT = os.environ.get("LDN_REFERENCE_ROOT", "/root/reference")
+# the upstream checkout, if there is one: named by LDN_REFERENCE_ROOT, else a `reference` directory beside this repository
+REF_ROOT = os.environ.get("LDN_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target, sources):

@@ -1,7 +1,7 @@
 """Generate tests/golden/ref_fallback.npz from the upstream reference's own pure-torch path.
 
-Run once in a container that has the upstream checkout (its location can be given in the environment
-variable LDN_REFERENCE_ROOT):   python tests/golden/make_golden.py
+Run once in a container that has the upstream checkout; its location must be given in the environment
+variable LDN_REFERENCE_ROOT:   LDN_REFERENCE_ROOT=/path/to/L_inf-dist-net-v2 python tests/golden/make_golden.py
 
 What it records, per case, are the inputs and the outputs of the reference functions
 `core.norm_dist.norm_dist(..., use_custom_cuda_func=False)` and
@@ -25,7 +25,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("LDN_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("LDN_REFERENCE_ROOT")
+if not REF or not os.path.isdir(os.path.join(REF, "core")):
+    sys.exit("set LDN_REFERENCE_ROOT to the upstream checkout")
 sys.modules.setdefault("norm_dist_cuda", types.ModuleType("norm_dist_cuda"))
 sys.path.insert(0, REF)
 from core.norm_dist import norm_dist, bound_inf_dist  # noqa: E402

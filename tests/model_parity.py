@@ -78,10 +78,12 @@ def check_training_step(kind, p, device, tol_out, tol_grad):
         ref = fx[f"{tag}/grad/{name}"]
         assert prm.grad is not None, (tag, name)
         got = prm.grad.cpu().numpy()
-        assert float(np.max(np.abs(got.astype(np.float64) - ref))) < tol_grad * whole, (tag, name)
+        err_abs = float(np.max(np.abs(got.astype(np.float64) - ref)))
+        assert err_abs < tol_grad * whole, (tag, name, err_abs / whole)
         if kind.endswith("_rand"):
             own = float(fx[f"{tag}/ref32_err/grad/{name}"]) if f"{tag}/ref32_err/grad/{name}" in fx.files else 0.0
-            assert rel_to_max(got, ref) < max(tol_grad, 4 * own), (tag, name)
+            err = rel_to_max(got, ref)
+            assert err < max(tol_grad, 4 * own), (tag, name, err)
     for name, m in net.named_modules():
         if isinstance(m, ldn.MeanShift):
             ref = fx[f"{tag}/running_mean/{name}"]
@@ -104,7 +106,11 @@ def check_certification(kind, device, exact):
         plain = net(x)
     for got, name in ((logits, "logits"), (worst, "worst"), (plain, "plain")):
         ref = fx[f"{kind}/certify/{name}"]
-        if exact:
+        if exact and name == "worst" and got.is_cuda:
+            # the margins are divided by 2 eps: torch's CUDA division by a scalar multiplies by the reciprocal, its
+            # CPU division (which made the fixture) divides, so the last bit may differ
+            assert rel_to_max(got.cpu().numpy(), ref) < 2.5e-7, (kind, name)
+        elif exact:
             assert np.array_equal(got.cpu().numpy(), ref), (kind, name)
         else:
             assert rel_to_max(got.cpu().numpy(), ref) < 1e-5, (kind, name)

@@ -5,8 +5,8 @@ main.py:304-318), on the real kernels.
 
 Tolerances: the operator-level bounds (integer p 1e-5, general p 1e-4 relative) apply per layer; through the two to
 three stacked distance layers of these models the outputs are held to 3e-5 (p = 8) / 1e-4 (p = 37.5) / 1e-5 (p = inf in
-training mode, where the batch mean of MeanShift is a float32 sum in another order) of the largest magnitude, all
-gradients to 1e-4.  The eval-mode p = inf MLP is subtract / max / elementwise only: logits and margins are bit-exact.
+training mode, where the batch mean of MeanShift is a float32 sum in another order) of the largest magnitude, the
+gradients to 3e-5 (p = 8), 3e-4 (p = 37.5: three stacked general-p backward passes of 1e-4 each) and 1e-5 (p = inf).  The eval-mode p = inf MLP is subtract / max / elementwise only: logits and margins are bit-exact.
 """
 import math
 
@@ -31,7 +31,8 @@ def device_ok():
 @pytest.mark.parametrize("p", mp.POWERS)
 def test_training_step_matches_reference_models(kind, p):
     tol_out = 1e-5 if math.isinf(p) else (3e-5 if p == 8.0 else 1e-4)
-    mp.check_training_step(kind, p, torch.device("cuda"), tol_out=tol_out, tol_grad=1e-4)
+    tol_grad = 1e-5 if math.isinf(p) else (3e-5 if p == 8.0 else 3e-4)
+    mp.check_training_step(kind, p, torch.device("cuda"), tol_out=tol_out, tol_grad=tol_grad)
 
 
 @pytest.mark.parametrize("kind", mp.KINDS)

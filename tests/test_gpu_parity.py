@@ -519,7 +519,8 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-@pytest.mark.parametrize("shape", [(64, 784, 1024, 1, 1), (130, 200, 150, 1, 1), (6, 36, 20, 2, 5), (512, 3072, 640, 1, 1)])
+@pytest.mark.parametrize("shape", [(64, 784, 1024, 1, 1), (130, 200, 150, 1, 1), (6, 36, 20, 2, 5), (512, 3072, 640, 1, 1),
+                                   (512, 3072, 5120, 1, 1)])
 def test_against_reference_cuda_kernels(C, shape):
     import ctypes
     ref = _ref_lib()
@@ -548,6 +549,39 @@ def test_against_reference_cuda_kernels(C, shape):
                                               *dims) == 0
     torch.cuda.synchronize()
     assert torch.equal(yL, yLr) and torch.equal(yU, yUr) and torch.equal(pL, pLr) and torch.equal(pU, pUr)
+    assert ref.ldn_ref_bound_inf_dist_forward_nograd(_ptr(xL), _ptr(xU), _ptr(w), _ptr(yLr), _ptr(yUr), *dims) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(yL, yLr) and torch.equal(yU, yUr)
+    # p = inf and bound backward: both sides scatter-add with atomics, so sums agree to rounding
+    g2 = dev(np.random.default_rng(12).standard_normal(g_np.shape).astype(np.float32))
+    gx, gw, gxr, gwr = (torch.full_like(t, float("nan")) for t in (x, w, x, w))
+    C.inf_dist_backward_input_weight(g, pos, gx, gw, G)
+    assert ref.ldn_ref_inf_dist_backward_input_weight(_ptr(g), _ptr(posr), _ptr(gxr), _ptr(gwr), *dims) == 0
+    torch.cuda.synchronize()
+    assert rel_to_max(gx.cpu().numpy(), gxr.cpu().numpy()) < 1e-5 and rel_to_max(gw.cpu().numpy(), gwr.cpu().numpy()) < 1e-5
+    gx.fill_(float("nan"))
+    C.inf_dist_backward_input(g, pos, gx, G)
+    assert ref.ldn_ref_inf_dist_backward_input(_ptr(g), _ptr(posr), _ptr(gxr), *dims) == 0
+    torch.cuda.synchronize()
+    assert rel_to_max(gx.cpu().numpy(), gxr.cpu().numpy()) < 1e-5
+    gxl, gxu, gxlr, gxur = (torch.full_like(x, float("nan")) for _ in range(4))
+    gw.fill_(float("nan"))
+    C.bound_inf_dist_backward_input_weight(g, g2, pL, pU, gxl, gxu, gw, G)
+    assert ref.ldn_ref_bound_inf_dist_backward_input_weight(_ptr(g), _ptr(g2), _ptr(pLr), _ptr(pUr), _ptr(gxlr),
+                                                            _ptr(gxur), _ptr(gwr), *dims) == 0
+    torch.cuda.synchronize()
+    for got, want in ((gxl, gxlr), (gxu, gxur), (gw, gwr)):
+        assert rel_to_max(got.cpu().numpy(), want.cpu().numpy()) < 1e-5
+    gxl.fill_(float("nan"))
+    gxu.fill_(float("nan"))
+    C.bound_inf_dist_backward_input(g, g2, pL, pU, gxl, gxu, G)
+    assert ref.ldn_ref_bound_inf_dist_backward_input(_ptr(g), _ptr(g2), _ptr(pLr), _ptr(pUr), _ptr(gxlr), _ptr(gxur),
+                                                     *dims) == 0
+    torch.cuda.synchronize()
+    for got, want in ((gxl, gxlr), (gxu, gxur)):
+        assert rel_to_max(got.cpu().numpy(), want.cpu().numpy()) < 1e-5
+    if CO > 1024:
+        return  # the finite-p part at the full width is covered by test_full_size_layer
     # finite p: outputs and both gradients within the stated tolerances
     for p in (8.0, 3.0, 9.0, 37.5):
         C.norm_dist_forward(x, w, y, G, p)

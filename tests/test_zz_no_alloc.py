@@ -1,10 +1,11 @@
-"""The allocation-free entry point (ldn_inf_dist_forward_nograd_noalloc) against the regular one.
+"""The allocation-free entry point (ldn_inf_dist_forward_nograd_noalloc) against the regular one and the CPU checker.
 
 Callers that may not allocate device memory while they run -- a server that gave its memory to its own pool
 at start-up, a runtime that forbids cudaMalloc after initialisation -- use this variant, whose scratch is a
-fixed array inside the library.  The results must be the same bits as ldn_inf_dist_forward_nograd, also on
-the second of two calls in a row (the array still holds what the first call left), and a problem whose
-scratch would not fit must be refused before anything runs.  The file name sorts last so that a run that
+fixed array inside the library.  The results must be the same bits as ldn_inf_dist_forward_nograd and as the CPU
+checker's, also on the second of two calls in a row (the array still holds what the first call left); the
+second call must leave the amount of free device memory as it found it; its status word must read 0; and a
+problem whose scratch would not fit must be refused before anything runs.  The file name sorts last so that a run that
 stops at the first failure has already run every other test.
 """
 import numpy as np
@@ -24,20 +25,28 @@ def _call(fn, x, w, y, G):
 def test_noalloc_matches_regular_entry_point_twice(shape):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
+    import oracle
     from l_inf_dist_net_v2_b200._lib import lib
     B, CI, CO, G, HW = shape
     gen = torch.Generator().manual_seed(42)
+    stream = torch.cuda.current_stream().cuda_stream
     for call in range(2):  # two calls in a row, different data, same fixed scratch
         x = torch.rand(B, CI, HW, generator=gen).cuda()
         w = torch.randn(CO, CI // G, generator=gen).cuda()
         y_ref = torch.full((B, CO, HW), float("nan"), device="cuda")
         y_new = torch.full((B, CO, HW), float("nan"), device="cuda")
         assert _call(lib.ldn_inf_dist_forward_nograd, x, w, y_ref, G) == 0
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         assert _call(lib.ldn_inf_dist_forward_nograd_noalloc, x, w, y_new, G) == 0
         torch.cuda.synchronize()
+        if call == 1:  # (the first call on a device may load the module that holds the array)
+            assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free call changed free device memory"
         # p = inf values are exact, so the tolerance the other tests use for them applies: identical bits
         assert torch.equal(y_ref, y_new), (shape, call)
-        assert np.isfinite(y_new.cpu().numpy()).all()
+        y_cpu, _ = oracle.inf_dist_forward(x.cpu().numpy(), w.cpu().numpy(), G, want_pos=False)
+        assert np.array_equal(y_new.cpu().numpy(), y_cpu), (shape, call)
+        assert lib.ldn_noalloc_check_status(stream) == 0
 
 
 def test_noalloc_refuses_problems_beyond_the_fixed_scratch():
