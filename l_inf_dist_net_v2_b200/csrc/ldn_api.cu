@@ -188,6 +188,7 @@ int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, c
     TileLaunch L;
     OpGeom geom{kTileN, 1};
     if (kind == FwdKind::PowInt || kind == FwdKind::PowGen || kind == FwdKind::PowNorm) geom = fwd_pow_geom(kind, ip);
+    else geom = fwd_inf_geom(kind);
     int r = fill_plan(c, &L, s.M, s.COg, s.CIg, s.G, fwd_acc_arrays(kind), geom);
     if (r != kOk) return r;
     TileParams& P = L.params;
@@ -365,7 +366,7 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
     const size_t xfloats = canonical_floats(s.CIg, s.M, s.G);
-    size_t need = 2 * pad256(xfloats * sizeof(float)) + w_scratch_bytes(w, s) + 2 * partial_bytes(cap_for(ctx), 3);
+    size_t need = 2 * pad256(xfloats * sizeof(float)) + w_scratch_bytes(w, s) + 2 * partial_bytes(cap_for(ctx), 5);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     float* lc = c.bump.take<float>(xfloats);
@@ -377,6 +378,13 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
     View wv;
     if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
     if (!pl) return run_forward(c, FwdKind::Bound, 0, lv, &uv, wv, s, yl, yu, nullptr, nullptr, nullptr, INFINITY);
+    if ((s.CIg + kTileK - 1) / kTileK <= kBoundBothMaxStages) {
+        // one pass: both bounds and the stage of each extremum, then the two index searches
+        r = run_forward(c, FwdKind::BoundPosBoth, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
+        if (r != kOk) return r;
+        if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st)) != kOk) return r;
+        return launch_rescan(2, as_operand(lv), as_operand(uv), as_operand(wv), yu, pu, s, c.st);
+    }
     r = run_forward(c, FwdKind::BoundPosLower, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
     if (r != kOk) return r;
     if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st)) != kOk) return r;

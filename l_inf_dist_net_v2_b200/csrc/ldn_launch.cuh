@@ -5,7 +5,8 @@
 
 namespace ldn {
 
-enum class FwdKind { PowInt, PowGen, PowNorm, Inf, InfPos, Bound, BoundPosLower, BoundPosUpper };
+enum class FwdKind { PowInt, PowGen, PowNorm, Inf, InfPos, Bound, BoundPosLower, BoundPosUpper, BoundPosBoth };
+constexpr int kBoundBothMaxStages = 65534;  // 16 bits per stage id (FwdBoundBoth)
 
 // number of accumulator arrays (float + int) an op keeps per output: sizes the stream-K scratch
 inline int fwd_acc_arrays(FwdKind k) {
@@ -14,10 +15,10 @@ inline int fwd_acc_arrays(FwdKind k) {
         case FwdKind::Bound: return 2;
         case FwdKind::BoundPosLower: return 3;
         case FwdKind::BoundPosUpper: return 3;
+        case FwdKind::BoundPosBoth: return 5;
         default: return 1;
     }
 }
-inline int fwd_num_a(FwdKind k) { return (k == FwdKind::Bound || k == FwdKind::BoundPosLower || k == FwdKind::BoundPosUpper) ? 2 : 1; }
 
 // tile width and resident CTAs per SM of the kernel a launch function will pick
 struct OpGeom {
@@ -29,12 +30,13 @@ constexpr OpGeom geom_of() {
     return OpGeom{16 * Op::REG_N, Op::CTAS_PER_SM};
 }
 OpGeom fwd_pow_geom(FwdKind kind, int ip);
+OpGeom fwd_inf_geom(FwdKind kind);
 OpGeom bwd_fused_geom(int iq);
 OpGeom bwd_x_geom(int iq);
 OpGeom bwd_w_geom(int iq);
 
 int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st);   // PowInt (ip 1..8), PowGen, PowNorm
-int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper}
+int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper,Both}
 // iq 0..8: integer p - 1; -1: general p with 1/y folded into the exponent offset; -2: general p, unfolded
 int launch_bwd_x(int iq, const TileLaunch& L, cudaStream_t st);
 int launch_bwd_w(int iq, const TileLaunch& L, cudaStream_t st);

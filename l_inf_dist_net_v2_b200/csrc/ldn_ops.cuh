@@ -322,18 +322,18 @@ template <bool POS>
 struct FwdInf : FwdLayout {
     static constexpr bool N_IN_SMEM = POS;  // frees 64 registers of the indexed kernel (0.83 -> 0.79 ms)
     static constexpr bool SHORT_STAGES = !POS;
-    static constexpr int UNROLL = 4;
+    static constexpr int UNROLL = 4;  // (128 x 64 tiles with two CTAs per SM: 0.556 ms against 0.548 ms)
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
     static constexpr bool PREFETCH = false;  // two 4-wide slabs would not fit the register file
-    // POS: f[0] = running maximum, f[1] = maximum inside the current 32-channel stage, n[0] = stage in which
-    // the running maximum last strictly increased (-1: never)
+    // POS: f[1] = running maximum, f[0] = its value when a stage last ended with a strict increase, n[0] = that stage
+    // (-1: never); the result is f[0] (== f[1] after the last stage)
     static constexpr int NUM_A = 1, NF = POS ? 2 : 1, NI = POS ? 1 : 0;
     static constexpr bool HAS_P = false;
     static constexpr bool STAGE_HOOK = POS;
     __device__ static void init(float* f, int* n) {
         f[0] = kEps;
         if (POS) {
-            f[1] = 0.0f;
+            f[1] = kEps;
             n[0] = -1;
         }
     }
@@ -341,8 +341,15 @@ struct FwdInf : FwdLayout {
     __device__ static void update(float* f, int*, float, const float* a, const float*, const float* b, int, int,
                                   const TileParams&) {
         float& m = f[POS ? 1 : 0];
+        // The subtraction is packed along k (both operands arrive as neighbouring registers of a 16-byte shared-memory
+        // read): one issue slot for two differences.  Every kernel of this family is bound by the issue rate
+        // (one warp instruction per scheduler and clock), not by a pipe; measured 0.572 -> 0.548 ms.
+        static_assert(KS % 2 == 0, "packed subtraction walks k in pairs");
 #pragma unroll
-        for (int k = 0; k < KS; ++k) m = fmaxf(m, fabsf(a[k] - b[k]));
+        for (int k = 0; k < KS; k += 2) {
+            const float2 d = pk_sub(make_float2(a[k], a[k + 1]), make_float2(b[k], b[k + 1]));
+            m = fmaxf(fmaxf(m, fabsf(d.x)), fabsf(d.y));
+        }
     }
     // end of a 32-channel stage: stages are visited in ascending order, so a strict comparison keeps the
     // first stage that reaches the final maximum
@@ -352,7 +359,6 @@ struct FwdInf : FwdLayout {
                 f[0] = f[1];
                 n[0] = stage;
             }
-            f[1] = 0.0f;
         }
     }
     __device__ static void combine(float* f, int* n, const float* pf, const int* pn) {
@@ -382,9 +388,9 @@ struct FwdInf : FwdLayout {
 // ------------------------------------------------------------------------------------------------
 struct FwdBound : FwdLayout {
     static constexpr bool SHORT_STAGES = true;
-    static constexpr int KSTEP = 4;  // measured best: 4-wide k-groups, no register double buffering, two per trip
+    static constexpr int KSTEP = 4;  // measured best: 4-wide k-groups, no register double buffering, one per trip
     static constexpr bool PREFETCH = false;
-    static constexpr int UNROLL = 2;
+    static constexpr int UNROLL = 1;  // packed subtractions (see FwdInf): 1.484 -> 1.418 ms
     static constexpr int NUM_A = 2, NF = 2, NI = 0;
     static constexpr bool HAS_P = false;
     __device__ static void init(float* f, int*) {
@@ -395,10 +401,14 @@ struct FwdBound : FwdLayout {
     __device__ static void update(float* f, int*, float, const float* lo, const float* up, const float* w, int, int,
                                    const TileParams&) {
 #pragma unroll
-        for (int k = 0; k < KS; ++k) {
-            const float t1 = w[k] - lo[k], t2 = up[k] - w[k];
-            f[0] = fminf(fminf(f[0], t1), t2);
-            f[1] = fmaxf(fmaxf(f[1], t1), t2);
+        for (int k = 0; k < KS; k += 2) {
+            const float2 w2 = make_float2(w[k], w[k + 1]);
+            const float2 t1 = pk_sub(w2, make_float2(lo[k], lo[k + 1]));
+            const float2 t2 = pk_sub(make_float2(up[k], up[k + 1]), w2);
+            f[0] = fminf(fminf(f[0], t1.x), t2.x);
+            f[1] = fmaxf(fmaxf(f[1], t1.x), t2.x);
+            f[0] = fminf(fminf(f[0], t1.y), t2.y);
+            f[1] = fmaxf(fmaxf(f[1], t1.y), t2.y);
         }
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) {
@@ -464,6 +474,75 @@ struct FwdBoundPos : FwdLayout {
             P.out_f0[off] = -f[0];
             P.out_i0[off] = pos;
         }
+    }
+};
+
+// Both bounds with both stage ids in one pass: four accumulators per output (running and current-stage minimum,
+// running and current-stage maximum) fit the register file on the 128 x 64 tile (32 outputs per thread).  The two
+// stage ids share one shared-memory word per output: bits 0..15 hold (stage of the minimum) + 1, bits 16..31
+// (stage of the maximum) + 1, 0 meaning "never improved"; reductions of more than 65534 stages take the two-pass
+// kernels above.
+struct FwdBoundBoth : FwdLayout {
+    static constexpr bool N_IN_SMEM = true;
+    static constexpr int REG_N = 4;
+    static constexpr int KSTEP = 4;
+    static constexpr int UNROLL = 1;
+    static constexpr bool PREFETCH = false;
+    // f[1] / f[3] = running minimum / maximum, f[0] / f[2] = their values when a stage last ended with a strict
+    // improvement; n[0] = the two 16-bit stage ids
+    static constexpr int NUM_A = 2, NF = 4, NI = 1;
+    static constexpr bool HAS_P = false;
+    static constexpr bool STAGE_HOOK = true;
+    static constexpr int kMaxStages = 65534;
+    __device__ static void init(float* f, int* n) {
+        f[0] = f[1] = -kEps;
+        f[2] = f[3] = kEps;
+        n[0] = 0;
+    }
+    template <int KS>
+    __device__ static void update(float* f, int*, float, const float* lo, const float* up, const float* w, int, int,
+                                  const TileParams&) {
+#pragma unroll
+        for (int k = 0; k < KS; k += 2) {
+            const float2 w2 = make_float2(w[k], w[k + 1]);
+            const float2 t1 = pk_sub(w2, make_float2(lo[k], lo[k + 1]));
+            const float2 t2 = pk_sub(make_float2(up[k], up[k + 1]), w2);
+            f[1] = fminf(fminf(f[1], t1.x), t2.x);
+            f[3] = fmaxf(fmaxf(f[3], t1.x), t2.x);
+            f[1] = fminf(fminf(f[1], t1.y), t2.y);
+            f[3] = fmaxf(fmaxf(f[3], t1.y), t2.y);
+        }
+    }
+    // the halves of the id word are written as 16-bit stores: no read-modify-write
+    __device__ static void stage_end(float* f, int* n, int stage) {
+        unsigned short* ids = reinterpret_cast<unsigned short*>(n);
+        if (f[1] < f[0]) {
+            f[0] = f[1];
+            ids[0] = static_cast<unsigned short>(stage + 1);
+        }
+        if (f[3] > f[2]) {
+            f[2] = f[3];
+            ids[1] = static_cast<unsigned short>(stage + 1);
+        }
+    }
+    __device__ static void combine(float* f, int* n, const float* pf, const int* pn) {
+        if (pf[0] < f[0]) {
+            f[0] = pf[0];
+            n[0] = (n[0] & static_cast<int>(0xffff0000u)) | (pn[0] & 0xffff);
+        }
+        if (pf[2] > f[2]) {
+            f[2] = pf[2];
+            n[0] = (n[0] & 0xffff) | (pn[0] & static_cast<int>(0xffff0000u));
+        }
+    }
+    __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
+    __device__ static void finalize(const float* f, const int* nn, float, int m, int n, int g, const TileParams& P) {
+        const long long off = out_offset(P.out, m, n, g);
+        P.out_f0[off] = -f[0];
+        P.out_f1[off] = f[2];
+        // stage ids (or -1); turned into the indices by rescan_kernel
+        P.out_i0[off] = (nn[0] & 0xffff) - 1;
+        P.out_i1[off] = static_cast<int>(static_cast<unsigned>(nn[0]) >> 16) - 1;
     }
 };
 

@@ -4,6 +4,7 @@ namespace ldn {
 
 namespace {
 constexpr int kBlock = 256;
+constexpr int kRescanChunk = 1024;  // outputs a block of rescan_kernel handles in one pass (a multiple of kBlock / 8)
 inline unsigned blocks_for(long long n) {
     long long b = (n + kBlock - 1) / kBlock;
     if (b < 1) b = 1;
@@ -153,61 +154,71 @@ __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __res
     }
 }
 
-// One thread per output element: 8 independent 16-byte loads per operand cover the recorded stage (operand
-// views are 16-byte aligned with row pitches that are multiples of 4 floats), then an in-register
-// descending scan keeps the lowest matching channel.
+// Eight lanes per output element: lane q of a group loads the q-th 16-byte piece of the recorded 32-channel stage of
+// each operand row (one full 128-byte line per group and operand: operand views are 16-byte aligned with row
+// pitches that are multiples of 4 floats), finds the lowest matching channel among its four, and a minimum over the
+// group's lanes keeps the lowest channel of the stage -- the index a strictly-greater scan in ascending order ends with.
+// blockIdx.x = (sample, group); blockIdx.y walks that pair's CO/G * HW outputs in chunks, so the index arithmetic
+// per output is one division by HW (none for fully connected layers) and, for those, a block keeps rereading one
+// input row, which stays in the L1 cache: only the weight pieces come from L2.
 __global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const float* __restrict__ y,
                               int* __restrict__ pos, Shape s) {
-    const long long total = static_cast<long long>(s.B) * s.CO * s.HW;
     const int kpad = (s.CIg + 3) & ~3;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int stage = pos[i];
-        int result = (mode == 1) ? static_cast<int>(0xffffffffu) : 0;
-        if (stage >= 0) {
-            const int hw = static_cast<int>(i % s.HW);
-            const long long t = i / s.HW;
-            const int o = static_cast<int>(t % s.COg);
-            const long long t2 = t / s.COg;
-            const int g = static_cast<int>(t2 % s.G);
-            const long long m = (t2 / s.G) * s.HW + hw;
-            const float* ar = a0.ptr + m * a0.stride_row + g * a0.stride_group;
-            const float* ur = a1.ptr + m * a1.stride_row + g * a1.stride_group;
-            const float* br = b.ptr + o * b.stride_row + g * b.stride_group;
-            const float yv = y[i];
-            const int k0 = stage * 32;
-            float4 av[8], bv[8], uv[8];
+    const int q = threadIdx.x & 7;
+    const int group_in_block = threadIdx.x >> 3;
+    const unsigned cohw = static_cast<unsigned>(s.COg) * static_cast<unsigned>(s.HW);  // < 2^31, checked by the launcher
+    const long long bg = blockIdx.x;
+    const int bi = static_cast<int>(bg / s.G), g = static_cast<int>(bg - static_cast<long long>(bi) * s.G);
+    const float* arow = a0.ptr + g * a0.stride_group;
+    const float* urow = a1.ptr + g * a1.stride_group;
+    const float* brow = b.ptr + g * b.stride_group;
+    // (the trip counts are the same for all lanes of a warp: its four groups handle consecutive outputs)
+    for (unsigned j0 = blockIdx.y * kRescanChunk; j0 < cohw; j0 += gridDim.y * kRescanChunk)
+        for (unsigned step = 0; step < kRescanChunk && j0 + step < cohw; step += kBlock / 8) {
+            const unsigned j = j0 + step + group_in_block;
+            const bool valid = j < cohw;
+            const long long i = bg * cohw + j;
+            const int stage = valid ? pos[i] : -1;
+            int best = 0x7fffffff;
+            if (stage >= 0) {
+                const unsigned o = s.HW == 1 ? j : j / static_cast<unsigned>(s.HW);
+                const unsigned hw = j - o * s.HW;
+                const long long m = static_cast<long long>(bi) * s.HW + hw;
+                const int k = stage * 32 + 4 * q;
+                if (k < kpad) {
+                    const float4 av = *reinterpret_cast<const float4*>(arow + m * a0.stride_row + k);
+                    const float4 bv = *reinterpret_cast<const float4*>(brow + o * b.stride_row + k);
+                    float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (mode != 0) uv = *reinterpret_cast<const float4*>(urow + m * a1.stride_row + k);
+                    const float yv = y[i];
+                    const float ae[4] = {av.x, av.y, av.z, av.w};
+                    const float be[4] = {bv.x, bv.y, bv.z, bv.w};
+                    const float ue[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int k = k0 + 4 * q;
-                const bool in = k < kpad;
-                av[q] = in ? *reinterpret_cast<const float4*>(ar + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-                bv[q] = in ? *reinterpret_cast<const float4*>(br + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-                if (mode != 0) uv[q] = in ? *reinterpret_cast<const float4*>(ur + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int q = 7; q >= 0; --q) {
-                const float ae[4] = {av[q].x, av[q].y, av[q].z, av[q].w};
-                const float be[4] = {bv[q].x, bv[q].y, bv[q].z, bv[q].w};
-                const float ue[4] = {uv[q].x, uv[q].y, uv[q].z, uv[q].w};
-#pragma unroll
-                for (int e = 3; e >= 0; --e) {
-                    const int k = k0 + 4 * q + e;
-                    bool hit, flag;
-                    if (mode == 0) {
-                        const float d = ae[e] - be[e];
-                        hit = fabsf(d) == yv;
-                        flag = d < 0.0f;
-                    } else {
-                        const float t1 = be[e] - ae[e], t2v = ue[e] - be[e];
-                        hit = (mode == 1) ? (fminf(t1, t2v) == -yv) : (fmaxf(t1, t2v) == yv);
-                        flag = !(t1 <= t2v);
+                    for (int e = 3; e >= 0; --e) {
+                        bool hit, flag;
+                        if (mode == 0) {
+                            const float d = ae[e] - be[e];
+                            hit = fabsf(d) == yv;
+                            flag = d < 0.0f;
+                        } else {
+                            const float t1 = be[e] - ae[e], t2v = ue[e] - be[e];
+                            hit = (mode == 1) ? (fminf(t1, t2v) == -yv) : (fmaxf(t1, t2v) == yv);
+                            flag = !(t1 <= t2v);
+                        }
+                        if (hit && k + e < s.CIg) best = ((k + e) << 1) | (flag ? 1 : 0);
                     }
-                    if (hit && k < s.CIg) result = k | (flag ? static_cast<int>(0x80000000u) : 0);
                 }
             }
+            best = min(best, __shfl_xor_sync(0xffffffffu, best, 1));
+            best = min(best, __shfl_xor_sync(0xffffffffu, best, 2));
+            best = min(best, __shfl_xor_sync(0xffffffffu, best, 4));
+            if (valid && q == 0) {
+                int result = (mode == 1) ? static_cast<int>(0xffffffffu) : 0;
+                if (best != 0x7fffffff) result = (best >> 1) | ((best & 1) ? static_cast<int>(0x80000000u) : 0);
+                pos[i] = result;
+            }
         }
-        pos[i] = result;
-    }
 }
 
 __global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles,
@@ -336,8 +347,13 @@ int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, co
 
 int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, int* pos, const Shape& s,
                   cudaStream_t st) {
-    const long long total = static_cast<long long>(s.B) * s.CO * s.HW;
-    rescan_kernel<<<blocks_for(total), kBlock, 0, st>>>(mode, a0, a1, b, y, pos, s);
+    const long long cohw = static_cast<long long>(s.COg) * s.HW;
+    const long long bg = static_cast<long long>(s.B) * s.G;
+    if (cohw > 0x7fffffffLL || bg > 0x7fffffffLL) return kBadArgument;
+    long long chunks = (cohw + kRescanChunk - 1) / kRescanChunk;
+    if (chunks > 65535) chunks = 65535;  // the kernel strides over the rest
+    rescan_kernel<<<dim3(static_cast<unsigned>(bg), static_cast<unsigned>(chunks)), kBlock, 0, st>>>(mode, a0, a1, b, y,
+                                                                                                      pos, s);
     LDN_LAUNCH_RET();
 }
 
