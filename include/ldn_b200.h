@@ -124,6 +124,23 @@ LDN_API int ldn_mean_shift_rows(const float* x, int B, int C, float* running_mea
  */
 LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long* lane_ops, ldn_stream_t stream);
 
+/*
+ * Parameter updates over a list of tensors in one kernel (the reference uses torch.optim.Adam with betas = (0.9, 0.99),
+ * eps = 1e-10, main.py:388-392; these follow torch.optim's update rules).  params / grads / state arrays are HOST
+ * arrays of `count` device pointers, sizes[t] the element count of tensor t; every gradient is multiplied by
+ * grad_scale first (1 / world size after a summing all-reduce, else 1).
+ *   ldn_adam_update: m = m + (g - m)(1 - beta1); v = v beta2 + (1 - beta2) g g;
+ *                    p = p - lr / (1 - beta1^step) * m / (sqrt(v) / sqrt(1 - beta2^step) + eps);   step counts from 1.
+ *   ldn_sgd_update:  g += weight_decay p; with momentum != 0: buf = first_step ? g : buf momentum + (1 - dampening) g,
+ *                    g = nesterov ? g + momentum buf : buf;  p = p - lr g.   momentum_buf may be NULL when momentum == 0.
+ */
+LDN_API int ldn_adam_update(int count, float* const* params, const float* const* grads, float* const* exp_avg,
+                            float* const* exp_avg_sq, const long long* sizes, float lr, float beta1, float beta2,
+                            float eps, int step, float grad_scale, ldn_stream_t stream);
+LDN_API int ldn_sgd_update(int count, float* const* params, const float* const* grads, float* const* momentum_buf,
+                           const long long* sizes, float lr, float momentum, float dampening, float weight_decay,
+                           int nesterov, int first_step, float grad_scale, ldn_stream_t stream);
+
 /* ---- finite p ------------------------------------------------------------------------------- */
 
 /*

@@ -33,6 +33,10 @@ SIGNATURES = {
                                                 [_c_float_p, _c_float_p, _c_float_p, _s],
     "ldn_inf_dist_forward_nograd_noalloc": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _s],
     "ldn_mean_shift_rows": [_c_float_p, _i, _i, _c_float_p, _f, _c_float_p, _c_float_p, _s],
+    "ldn_adam_update": [_i, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                        _f, _f, _f, _f, _i, _f, _s],
+    "ldn_sgd_update": [_i, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                       _f, _f, _f, _f, _i, _i, _f, _s],
     "ldn_check_status": [_s],
     "ldn_noalloc_check_status": [_s],
     "ldn_release_scratch": [],

@@ -5,7 +5,8 @@ DistributedDataParallel does in the reference (main.py:357), and the averaging o
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_bounds", "shard_batch", "allreduce_mean_", "average_scalars"]
+__all__ = ["shard_bounds", "shard_batch", "allreduce_mean_", "average_scalars", "OverlappedDataParallel",
+           "nccl_group_with_cta_limit"]
 
 
 def shard_bounds(n, rank, world):
@@ -70,3 +71,111 @@ def average_scalars(*values, device=None, group=None):
         dist.all_reduce(t, group=group)
         t /= dist.get_world_size(group)
     return t.tolist()
+
+
+def nccl_group_with_cta_limit(max_ctas):
+    """A second NCCL process group over all ranks whose collectives use at most `max_ctas` CTAs, so that they can run
+    on the SMs the distance kernels are told to leave free (OverlappedDataParallel(reserve_sms=...))."""
+    opts = dist.ProcessGroupNCCL.Options()
+    opts.config.max_ctas = int(max_ctas)
+    opts.config.min_ctas = 1
+    return dist.new_group(backend="nccl", pg_options=opts)
+
+
+class OverlappedDataParallel:
+    """Data-parallel training with DistributedDataParallel's semantics (main.py:357: every rank applies the mean of all
+    ranks' gradients) and the gradient exchange hidden behind the next step's forward pass.
+
+    At p = inf a layer's backward pass is a scatter of a few hundred microseconds while its weight gradient is
+    60-100 MB, so there is no backward work to hide the all-reduce behind.  Instead:
+
+      * each parameter's all-reduce (mean) starts from a gradient hook as soon as that gradient is complete;
+      * `step()` only marks the updates as due; a layer's own optimiser applies its update in a forward pre-hook, just
+        before that layer is used again, after waiting for that layer's all-reduce only.  The last layers' collectives
+        (issued first during backward) thus run beside the first layers' forward kernels of the next step.  The values
+        every layer computes with are exactly those of the usual "all-reduce, then step" order;
+      * while collectives are in flight the persistent distance kernels leave `reserve_sms` SMs free
+        (ldn_set_max_ctas), which is where a CTA-limited NCCL group (nccl_group_with_cta_limit) runs.
+
+    `optimizer_factory(params)` builds one optimiser per layer (any torch.optim optimiser, or optim.FusedAdam /
+    FusedSGD).  Call `finish()` before evaluating, checkpointing or reading parameters: it applies what is still due
+    and, like DistributedDataParallel's buffer broadcast, copies rank 0's buffers (MeanShift running means) to all ranks.
+    """
+
+    def __init__(self, model, optimizer_factory, group=None, reserve_sms=0, set_max_ctas=None):
+        self.model = model
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.reserve_sms = reserve_sms if self.world > 1 else 0
+        self._set_max_ctas = set_max_ctas
+        self._sm_count = None
+        self._capped = False
+        self.units = []
+        self.exchange = self.world > 1
+        avg = self.world > 1 and dist.get_backend(group) == "nccl"
+        for module in model.modules():
+            params = [q for q in module.parameters(recurse=False) if q.requires_grad]
+            if not params:
+                continue
+            unit = {"module": module, "params": params, "optimizer": optimizer_factory(params), "pending": [],
+                    "due": False}
+            self.units.append(unit)
+            module.register_forward_pre_hook(lambda mod, args, u=unit: self._apply(u))
+            for q in params:
+                q.register_post_accumulate_grad_hook(lambda prm, u=unit, a=avg: self._grad_ready(u, prm, a))
+
+    # -- hooks ----------------------------------------------------------------------------------------------------
+    def _grad_ready(self, unit, prm, avg):
+        if not self.exchange:
+            return
+        op = dist.ReduceOp.AVG if avg else dist.ReduceOp.SUM
+        work = dist.all_reduce(prm.grad, op=op, group=self.group, async_op=True)
+        unit["pending"].append((work, None if avg else prm))
+        self._cap(True)
+
+    def _cap(self, on):
+        if self.reserve_sms <= 0 or on == self._capped:
+            return
+        if self._set_max_ctas is None:
+            from ._lib import lib
+            self._set_max_ctas = lib.ldn_set_max_ctas
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        self._set_max_ctas(self._sm_count - self.reserve_sms if on else 0)
+        self._capped = on
+
+    def _apply(self, unit):
+        if not unit["due"]:
+            return
+        for work, summed in unit["pending"]:
+            work.wait()
+            if summed is not None:  # backends without an averaging reduction
+                summed.grad.div_(self.world)
+        unit["pending"].clear()
+        unit["optimizer"].step()
+        for q in unit["params"]:
+            q.grad = None
+        unit["due"] = False
+        if self._capped and not any(not w.is_completed() for u in self.units for w, _ in u["pending"]):
+            self._cap(False)
+
+    # -- training-loop interface ------------------------------------------------------------------------------------
+    def step(self):
+        """After backward: every layer's update becomes due (applied before the layer's next forward, or by finish())."""
+        for unit in self.units:
+            unit["due"] = True
+
+    def finish(self):
+        for unit in self.units:
+            self._apply(unit)
+        self._cap(False)
+        if self.world > 1:
+            bufs = [b for b in self.model.buffers()]
+            if bufs:
+                flat = torch.cat([b.reshape(-1).float() for b in bufs])
+                dist.broadcast(flat, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                               group=self.group)
+                off = 0
+                for b in bufs:
+                    b.copy_(flat[off:off + b.numel()].view_as(b))
+                    off += b.numel()
