@@ -60,10 +60,15 @@ def parse_args():
                          "steps of a 6-layer distance MLP (depth 6, width 5120, 3x32x32 inputs, 10 classes); "
                          "hybrid-*: 5 distance layers (width 5120) + interval-bound linear head (hidden 512)")
     ap.add_argument("--certify-samples", type=int, default=50000)
-    ap.add_argument("--overlap-sms", type=int, default=0,
-                    help="mlp-train with N > 1: start each parameter's all-reduce as soon as its gradient is ready and "
-                         "keep this many SMs free of the persistent tile kernels during backward so that the "
-                         "collective can run beside them (0: all-reduce after backward)")
+    ap.add_argument("--reserve-sms", type=int, default=8,
+                    help="N > 1, model steps: SMs the persistent distance kernels leave free while gradient collectives "
+                         "are in flight; the collectives run in an NCCL group limited to as many CTAs (0: no limit)")
+    ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"],
+                    help="model training workloads: Adam as the reference driver uses it, or plain SGD lr 0.02")
+    ap.add_argument("--model-global-batch", type=int, default=4096)
+    ap.add_argument("--no-model", action="store_true", help="skip the model-level block of the default run")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long back-to-back block")
+    ap.add_argument("--sustained-steps", type=int, default=1000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     return ap.parse_args()
@@ -182,7 +187,7 @@ def event_ms_list(fn, steps, warmup, flush):
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
 
-def run_ours(args, rank, world, local_rank):
+def run_ours(args, rank, world, local_rank, comm_group=None):
     import torch.distributed as dist
     import l_inf_dist_net_v2_b200 as ldn
     from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
@@ -330,6 +335,40 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, total_e2e = float(t[0]), float(t[1])
 
+    # ---- the same step back to back for seconds: what the clocks settle at under a sustained load ---------------
+    sustained = None
+    if not args.no_sustained:
+        s2 = ClockSampler(local_rank)
+        s2.start()
+        for _ in range(3):
+            flush()
+            step()
+        torch.cuda.synchronize()
+        barrier()
+        s2.mark()
+        ms_s = event_ms_list(step, args.sustained_steps, 0, flush)
+        torch.cuda.synchronize()
+        barrier()
+        ck = s2.stop()
+        tot = sum(ms_s)
+        if world > 1:
+            t = torch.tensor([tot], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            tot = float(t[0])
+        n = args.sustained_steps
+        tail = sorted(ms_s[n // 2:])
+        sustained = {"steps": n, "seconds": round(tot * 1e-3, 3), "ms_per_step": round(tot / n, 4),
+                     "ms_per_step_second_half_median": round(tail[len(tail) // 2], 4),
+                     "value": round(world * pairs * n / (tot * 1e-3) / 1e9, 2), "unit": UNIT, "clocks": ck}
+
+    model = None
+    if not args.no_model:
+        try:
+            model = model_block(args, rank, world, local_rank, comm_group)
+        except Exception as exc:  # the headline line must survive a failure here
+            model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        C.check_status()
+
     if rank != 0:
         return None
 
@@ -425,13 +464,16 @@ def run_ours(args, rank, world, local_rank):
             rows.append(row)
         return rows
 
-    # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
-    # under profiles/; only valid for that shape and p
-    ncu_traffic = {}
-    if (B, CI, CO) == (512, 3072, 5120):
-        ncu_traffic = {"8": {"forward": 75.8e6, "backward_fused": 406.5e6},
-                       "37.5": {"forward": 94.2e6, "backward_fused": 467.5e6},  # forward: the sum pass
-                       "inf": {"forward": 98.7e6}}.get(args.p, {})
+    # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) as captured with ncu: read from
+    # profiles/dram_traffic.json, which names the capture command and the source revision; only valid for its shape
+    ncu_traffic, traffic_source = {}, None
+    try:
+        tj = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))
+        if tj.get("shape") == [B, CI, CO]:
+            ncu_traffic = tj.get("p", {}).get(args.p, {})
+            traffic_source = f"profiles/dram_traffic.json ({tj.get('captured')}, source revision {tj.get('revision')})"
+    except Exception:
+        pass
     rows = kernel_rows(p, args.p, max(10, min(args.steps, 30)))
     in_step = [r for r in rows if r["kernel"] in (("forward", "grad_input", "grad_weight") if fam == "inf"
                                                  else ("forward", "backward_fused"))]
@@ -458,6 +500,7 @@ def run_ours(args, rank, world, local_rank):
             "slots_per_pair": dominant["slots_per_pair"], "ms": dominant["ms"],
             "frac_of_instruction_mix_probe": dominant.get("tile_kernel_frac_of_mix_probe"),
             "traffic": ncu_traffic.get(dominant["kernel"]), "traffic_unit": "bytes per launch (ncu)",
+            "traffic_source": traffic_source,
             "algorithmic_bytes": (4 * (B * CO + B * CI + CO * CI) + 4 * (B * CI + CO * CI))
             if dominant["kernel"] == "backward_fused" else 4 * (B * CI + CO * CI + B * CO)}
     else:
@@ -466,6 +509,22 @@ def run_ours(args, rank, world, local_rank):
             "peak": hbm_peak, "unit": "GB/s", "frac": round(dominant["gb_per_s"] / hbm_peak, 3),
             "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s", "ms": dominant["ms"],
             "traffic": None}
+    if sustained is not None:
+        # whole step (forward + both gradients) in algorithmic lane-instructions, at the clock that held
+        fam_slots = {"int": 4 + SLOTS_FUSED, "general": 6 + SLOTS_FUSED, "inf": 2}[fam]
+        ach = fam_slots * pairs / (sustained["ms_per_step"] * 1e-3) / 1e12
+        mhz = sustained["clocks"].get("sm_mhz")
+        sustained.update({"slots_per_pair_per_step": fam_slots, "step_tlaneop_per_s": round(ach, 2),
+                          "frac_of_nominal_at_max_clock": round(ach / nominal_fp32, 3),
+                          "frac_of_nominal_at_sampled_clock":
+                              round(ach / (sms * SM_LANES * mhz * 1e6 / 1e12), 3) if mhz else None,
+                          "ms_x_mhz": round(sustained["ms_per_step"] * mhz, 1) if mhz else None,
+                          "ffma_probe_tlaneop_per_s": round(ffma_peak, 2),
+                          "note": "the FFMA probe ran after this block at whatever clock the GPU then held; "
+                                  "frac_of_nominal_at_sampled_clock uses the median SM clock sampled during this block"})
+        line["sustained"] = sustained
+    if model is not None:
+        line["model"] = model
     line["kernels"] = rows
     line["probes"] = {"ffma_tlaneop_per_s": round(ffma_peak, 2), "mufu_top_per_s": round(mufu_peak, 3),
                       "general_p_mix_bwd_tpair_per_s": round(mix_bwd_peak, 3),
@@ -501,201 +560,246 @@ def run_ours(args, rank, world, local_rank):
 
 
 # ------------------------------------------------------------------------------------------------
-# Extra workloads: a 6-layer distance MLP built from this package's modules, with the layer sizes, initialisation,
-# loss and margin computation of the reference's MLPModel recipe (ell_inf_models.py:16-46, main.py:304-310)
+# Model-level workloads: the reference's MLPModel / HybridModel recipes (ell_inf_models.py:16-75) on this package's
+# models, losses (main.py:304-318) and optimisers; tests/test_gpu_models.py pins these classes to the reference
 # ------------------------------------------------------------------------------------------------
-def build_mlp(depth, width, pixels, classes, p, device):
+IMAGE = [3, 32, 32]
+
+
+def build_model(kind, p, device):
+    """kind "mlp": MLPModel(depth=6, width=5120, identity_val=10.0); "hybrid": HybridModel(depth=7, width=5120,
+    hidden=512, identity_val=10.0); random initial weights (seed 0 on every rank)."""
     import l_inf_dist_net_v2_b200 as ldn
     torch.manual_seed(0)
-    layers = [ldn.NormDist(pixels, width, bias=False, mean_shift=True, std=1.0, identity_val=10.0)]
-    for _ in range(depth - 2):
-        layers.append(ldn.NormDist(width, width, bias=False, mean_shift=True, std=1.0, identity_val=10.0))
-    layers.append(ldn.NormDist(width, classes, bias=True, mean_shift=False, std=1.0, identity_val=10.0))
-    net = torch.nn.ModuleList(layers).to(device)
-    for m in net:
-        m.p = p
+    with torch.device(device):
+        if kind == "mlp":
+            net = ldn.MLPModel(depth=6, width=5120, input_dim=IMAGE, identity_val=10.0)
+        else:
+            net = ldn.HybridModel(depth=7, width=5120, input_dim=IMAGE, hidden=512, identity_val=10.0)
+    ldn.set_p_norm(net, p)
     return net
 
 
-def mlp_forward(net, x, lower=None, upper=None):
-    paras = (x, lower, upper)
-    for m in net:
-        paras = m(*paras)
-    return paras
+def make_optimizer_factory(name):
+    from l_inf_dist_net_v2_b200.optim import FusedAdam, FusedSGD
+    if name == "sgd":
+        return (lambda params: FusedSGD(params, lr=0.02)), "SGD lr 0.02 (one-kernel update)"
+    return (lambda params: FusedAdam(params, lr=0.03, betas=(0.9, 0.99), eps=1e-10)), \
+        "Adam lr 0.03 betas (0.9, 0.99) eps 1e-10 as main.py:388-392 (one-kernel update)"
 
 
-class IntervalHead(torch.nn.Module):
-    """Interval-bound head of the reference's HybridModel (ell_inf_models.py:49-75 with BoundLinear, BoundTanh,
-    BoundFinalLinear of core/modules/basic_modules.py:27-46, :16-18, :77-101), written in centre / radius form:
-    a scaled linear layer maps centre c and radius r to (W c + b, |W| r); tanh is monotone; the last layer
-    returns, per sample, the worst-case logit differences against the target class."""
+class TrainStep:
+    """One training step as the reference's train() runs it (main.py:76-91): batch from pinned host memory, forward
+    with targets, loss, backward, gradient exchange, optimiser step; the loss value goes back to the host."""
 
-    def __init__(self, width, hidden, classes):
-        super().__init__()
-        self.w1 = torch.nn.Parameter(torch.randn(hidden, width))
-        self.b1 = torch.nn.Parameter(torch.zeros(hidden))
-        self.w2 = torch.nn.Parameter(torch.randn(classes, hidden))
-        self.b2 = torch.nn.Parameter(torch.zeros(classes))
-        self.s1, self.s2 = 1.0 / math.sqrt(width), 1.0 / math.sqrt(hidden)
+    def __init__(self, kind, p, batch, rank, world, device, optimizer="adam", reserve_sms=0, comm_group=None,
+                 eps=None):
+        import l_inf_dist_net_v2_b200 as ldn
+        from l_inf_dist_net_v2_b200.parallel import OverlappedDataParallel
+        self.net = build_model(kind, p, device)
+        self.net.train()
+        self.loss_fn = ldn.losses.hinge(mix=0.25) if kind == "mlp" else ldn.losses.crossentropy(mix=0)
+        self.eps = eps if eps is not None else (8.0 / 255.0 if kind == "mlp" else 0.0345)
+        factory, self.optimizer_name = make_optimizer_factory(optimizer)
+        # first layer's exchange (exposed) on the default group at full width, the rest on the CTA-limited group
+        self.ddp = OverlappedDataParallel(self.net, factory, group=comm_group,
+                                          first_group=torch.distributed.group.WORLD if comm_group is not None else None,
+                                          reserve_sms=reserve_sms)
+        gen = torch.Generator().manual_seed(1000 + rank)
+        self.xh = torch.rand(batch, *IMAGE, generator=gen).pin_memory()
+        self.th = torch.randint(0, 10, (batch,), generator=gen).pin_memory()
+        self.x = torch.empty(batch, *IMAGE, device=device)
+        self.t = torch.empty(batch, dtype=torch.long, device=device)
+        self.loss_h = torch.zeros(1).pin_memory()
+        self.h2d = self.xh.numel() * 4 + self.th.numel() * 8
+        self.d2h = 4
 
-    def forward(self, x, lower, upper, targets):
-        centre, radius = (lower + upper) * 0.5, (upper - lower) * 0.5
-        h = torch.addmm(self.b1, x, self.w1.t(), alpha=self.s1)
-        hc = torch.addmm(self.b1, centre, self.w1.t(), alpha=self.s1)
-        hr = torch.mm(radius, self.w1.abs().t()) * self.s1
-        h, hl, hu = torch.tanh(h), torch.tanh(hc - hr), torch.tanh(hc + hr)
-        logits = torch.addmm(self.b2, h, self.w2.t(), alpha=self.s2)
-        dw = self.w2.unsqueeze(0) - self.w2.index_select(0, targets).unsqueeze(1)      # B x classes x hidden
-        db = self.b2.unsqueeze(0) - self.b2.index_select(0, targets).unsqueeze(1)      # B x classes
-        c2, r2 = (hl + hu) * 0.5, (hu - hl) * 0.5
-        worst = (dw.bmm(c2.unsqueeze(-1)) + dw.abs().bmm(r2.unsqueeze(-1))).squeeze(-1) * self.s2 + db
-        return logits, worst
+    def __call__(self):
+        self.x.copy_(self.xh, non_blocking=True)
+        self.t.copy_(self.th, non_blocking=True)
+        logits, worst = self.net(self.x, targets=self.t, eps=self.eps)
+        loss = self.loss_fn(logits, worst, self.t)
+        loss.backward()
+        self.ddp.step()
+        self.loss_h.copy_(loss.detach().view(1), non_blocking=True)
+
+    def finish(self):
+        self.ddp.finish()
 
 
-def hinge_loss(outputs, lower, upper, targets, eps, mix=0.25):
-    # margins of the negated distances: upper bound of the others minus lower bound of the target
-    x, lo, up = -outputs, -upper, -lower
-    margin = up - torch.gather(lo, 1, targets.view(-1, 1))
-    margin = margin.scatter(1, targets.view(-1, 1), 0) / (2 * eps)
-    res = margin.clamp(min=0)
-    return (1 - mix) * res.max(dim=1)[0].mean() + mix * res.mean()
+class CertifySweep:
+    """The certification pass of main.py:182-215 over `samples` synthetic test images in batches of `batch`: eval
+    mode, p = inf, value and interval bounds (eps = 8/255, box [0, 1]) through every layer, clean and certified
+    correct counts accumulated on the device; the last batch may be ragged."""
+
+    def __init__(self, kind, samples, batch, rank, device):
+        self.net = build_model(kind, math.inf, device)
+        self.net.eval()
+        self.samples, self.batch = samples, batch
+        gen = torch.Generator().manual_seed(2000 + rank)
+        self.xh = torch.rand(batch, *IMAGE, generator=gen).pin_memory()
+        self.th = torch.randint(0, 10, (batch,), generator=gen).pin_memory()
+        self.x = torch.empty(batch, *IMAGE, device=device)
+        self.t = torch.empty(batch, dtype=torch.long, device=device)
+        self.up = torch.ones(3, 1, 1, device=device)
+        self.down = torch.zeros(3, 1, 1, device=device)
+        self.counts = torch.zeros(2, device=device)
+        self.counts_h = torch.zeros(2).pin_memory()
+        self.batches = (samples + batch - 1) // batch
+        self.h2d = self.xh.numel() * 4 + self.th.numel() * 8
+
+    def one_batch(self, n):
+        self.x.copy_(self.xh, non_blocking=True)
+        self.t.copy_(self.th, non_blocking=True)
+        x, t = self.x[:n], self.t[:n]
+        with torch.no_grad():
+            logits, worst = self.net(x, targets=t, eps=8.0 / 255.0, up=self.up, down=self.down)
+            self.counts[0] += (logits.argmax(1) == t).sum()
+            self.counts[1] += (worst.argmax(1) == t).sum()
+
+    def __call__(self):
+        self.counts.zero_()
+        left = self.samples
+        for _ in range(self.batches):
+            self.one_batch(min(self.batch, left))
+            left -= self.batch
+        self.counts_h.copy_(self.counts, non_blocking=True)
 
 
-def run_mlp(args, rank, world, local_rank):
+def _timed(fn, reps, world, dev):
+    """reps calls of fn between two CUDA events, bracketed by barriers; max over ranks, in ms."""
     import torch.distributed as dist
-    from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
-    from l_inf_dist_net_v2_b200._lib import lib
-    from l_inf_dist_net_v2_b200.parallel import allreduce_mean_
-
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    train = args.workload.endswith("train")
-    hybrid = args.workload.startswith("hybrid")
-    p = p_value(args.p) if train else math.inf
-    B = args.batch
-    if hybrid:
-        # five distance layers 3072 -> 5120 -> ... -> 5120, all with mean shift and without bias
-        net = build_mlp(6, 5120, 3072, 5120, p, dev)[:5]
-        torch.manual_seed(1)
-        head = IntervalHead(5120, 512, 10).to(dev)
-    else:
-        net = build_mlp(6, 5120, 3072, 10, p, dev)
-        head = None
-    gen = torch.Generator().manual_seed(1000 + rank)
-    eps = 8.0 / 255.0
-    sampler = ClockSampler(local_rank)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-
-    if train:
-        xh = torch.rand(B, 3, 32, 32, generator=gen).pin_memory()
-        th = torch.randint(0, 10, (B,), generator=gen).pin_memory()
-        x_dev = torch.empty(B, 3072, device=dev)
-        t_dev = torch.empty(B, dtype=torch.long, device=dev)
-        params = [q for q in net.parameters()] + ([q for q in head.parameters()] if hybrid else [])
-        opt = torch.optim.SGD(params, lr=0.02)
-        eps_train = 0.0345
-        net.train()
-        loss_h = torch.zeros(1).pin_memory()
-        overlap = world > 1 and args.overlap_sms > 0
-        pending = []
-        if overlap:
-            sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            for q in params:
-                q.register_post_accumulate_grad_hook(
-                    lambda prm: pending.append(dist.all_reduce(prm.grad, async_op=True)))
-
-        def step():
-            x_dev.copy_(xh.view(B, -1), non_blocking=True)
-            t_dev.copy_(th, non_blocking=True)
-            opt.zero_grad(set_to_none=True)
-            out, _, _ = mlp_forward(net, x_dev)
-            if hybrid:
-                _, worst = head(out, out - eps_train, out + eps_train, t_dev)
-                loss = torch.nn.functional.cross_entropy(worst, t_dev)
-            else:
-                loss = hinge_loss(out, out - eps, out + eps, t_dev, eps)
-            if overlap:
-                lib.ldn_set_max_ctas(sms - args.overlap_sms)
-                loss.backward()
-                lib.ldn_set_max_ctas(0)
-                for h in pending:
-                    h.wait()
-                pending.clear()
-                torch._foreach_div_([q.grad for q in params if q.grad is not None], world)
-            else:
-                loss.backward()
-                if world > 1:
-                    allreduce_mean_([q.grad for q in params if q.grad is not None])
-            opt.step()
-            loss_h.copy_(loss.detach().view(1), non_blocking=True)
-
-        per_step_samples = B
-        h2d, d2h = xh.numel() * 4 + th.numel() * 8, 4
-    else:
-        n_local = args.certify_samples // world
-        batches = (n_local + B - 1) // B
-        xh = torch.rand(B, 3, 32, 32, generator=gen).pin_memory()
-        th = torch.randint(0, 10, (B,), generator=gen).pin_memory()
-        x_dev = torch.empty(B, 3072, device=dev)
-        t_dev = torch.empty(B, dtype=torch.long, device=dev)
-        net.eval()
-        res_h = torch.zeros(B, 10).pin_memory()
-
-        def step():  # one certification batch: value and interval bounds through every distance layer
-            x_dev.copy_(xh.view(B, -1), non_blocking=True)
-            t_dev.copy_(th, non_blocking=True)
-            with torch.no_grad():
-                out, lo, up = mlp_forward(net, x_dev, (x_dev - eps).clamp(min=0), (x_dev + eps).clamp(max=1))
-                if hybrid:
-                    _, lo = head(out, lo, up, t_dev)
-            res_h.copy_(lo, non_blocking=True)
-
-        per_step_samples = B
-        h2d, d2h = xh.numel() * 4, res_h.numel() * 4
-        args.steps = min(args.steps, batches) if args.steps else batches
-
-    sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step()
     torch.cuda.synchronize()
-    barrier()
-    sampler.mark()
-    launches0 = lib.ldn_kernel_launches()
+    if world > 1:
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(reps):
+        fn()
     e1.record()
     torch.cuda.synchronize()
-    barrier()
-    launches = int(lib.ldn_kernel_launches() - launches0)
-    clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
     ms = e0.elapsed_time(e1)
-    C.check_status()
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
+    return ms
+
+
+def model_block(args, rank, world, local_rank, comm_group):
+    """Configuration 5 of the benchmark set: HybridModel(depth=7, width=5120, hidden=512) at p = inf, one training
+    step on a global batch of 4096 split over the ranks (main.py:346-348) with the gradient exchange, and the
+    50 000-sample certification sweep sharded over the ranks."""
+    import torch.distributed as dist
+    from l_inf_dist_net_v2_b200._lib import lib
+    dev = torch.device("cuda", local_rank)
+    out = {}
+    gb = args.model_global_batch
+    if gb % world != 0:
+        return {"error": f"global batch {gb} is not divisible by {world} ranks"}
+    step = TrainStep("hybrid", math.inf, gb // world, rank, world, dev, optimizer="adam",
+                     reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group)
+    reps = 10 if world == 1 else 20
+    launches0 = lib.ldn_kernel_launches()
+    for _ in range(3):
+        step()
+    ms = _timed(step, reps, world, dev)
+    launches = int(lib.ldn_kernel_launches() - launches0) // (reps + 3)
+    row = {"model": "HybridModel(depth=7, width=5120, hidden=512, identity_val=10.0), p=inf, cross-entropy on "
+                    "worst-case logits, eps_train 0.0345",
+           "global_batch": gb, "batch_per_rank": gb // world, "steps": reps, "ms_per_step": round(ms / reps, 3),
+           "samples_per_s": round(gb * reps / (ms * 1e-3), 1), "optimizer": step.optimizer_name,
+           "library_kernels_per_step": launches, "h2d_bytes_per_step": step.h2d, "d2h_bytes_per_step": step.d2h,
+           "exchange": "none" if world == 1 else
+           f"NCCL all-reduce (mean) per parameter, started after backward in forward order, each layer's update deferred "
+           f"to just before its next forward; {args.reserve_sms} SMs left free by the distance kernels while "
+           f"collectives are in flight"}
+    if world > 1:
+        step.ddp.exchange = False  # same step without the collectives: what the exchange costs
+        for _ in range(2):
+            step()
+        ms0 = _timed(step, reps, world, dev)
+        step.ddp.exchange = True
+        row["ms_per_step_without_exchange"] = round(ms0 / reps, 3)
+        row["exposed_exchange_ms"] = round((ms - ms0) / reps, 3)
+    step.finish()
+    out["hybrid_train"] = row
+    del step
+    torch.cuda.empty_cache()
+    n_local = args.certify_samples // world
+    sweep = CertifySweep("hybrid", n_local, 512, rank, dev)
+    sweep.one_batch(512)
+    sweep.one_batch(512)
+    ms = _timed(sweep, 1, world, dev)
+    counts = sweep.counts_h.clone().to(dev)
+    if world > 1:
+        dist.all_reduce(counts)  # main.py:207
+    out["hybrid_certify"] = {
+        "model": "HybridModel(depth=7, width=5120, hidden=512), eval mode, p=inf, value + interval bounds, eps=8/255",
+        "samples": n_local * world, "samples_per_rank": n_local, "batch": 512, "batches_per_rank": sweep.batches,
+        "seconds": round(ms * 1e-3, 4), "samples_per_s": round(n_local * world / (ms * 1e-3), 1),
+        "h2d_bytes_per_batch": sweep.h2d, "clean_correct": int(counts[0]), "certified_correct": int(counts[1])}
+    del sweep
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_model(args, rank, world, local_rank, comm_group):
+    """--workload mlp-train | mlp-certify | hybrid-train | hybrid-certify: the model-level step as the headline."""
+    import torch.distributed as dist
+    from l_inf_dist_net_v2_b200 import norm_dist_cuda as C
+    from l_inf_dist_net_v2_b200._lib import lib
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    kind, what = args.workload.split("-")
+    train = what == "train"
+    B = args.batch
+    sampler = ClockSampler(local_rank)
+    if train:
+        p = p_value(args.p)
+        step = TrainStep(kind, p, B, rank, world, dev, optimizer=args.optimizer,
+                         reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group)
+        h2d, d2h = step.h2d, step.d2h
+        per_step = B
+    else:
+        n_local = args.certify_samples // world
+        sweep = CertifySweep(kind, n_local, B, rank, dev)
+        step = lambda: sweep.one_batch(B)  # noqa: E731
+        h2d, d2h = sweep.h2d, 8
+        per_step = B
+        args.steps = min(args.steps, sweep.batches) if args.steps else sweep.batches
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler.mark()
+    launches0 = lib.ldn_kernel_launches()
+    ms = _timed(step, args.steps, world, dev)
+    launches = int(lib.ldn_kernel_launches() - launches0)
+    clocks = sampler.stop()
+    if train:
+        step.finish()
+    C.check_status()
     if rank != 0:
         return None
-    value = world * per_step_samples * args.steps / (ms * 1e-3)
+    value = world * per_step * args.steps / (ms * 1e-3)
     name = args.workload.replace("-", "_") + "_samples_per_s"
-    model = ("5 distance layers (3072-5120x5) + interval-bound head 5120-512-10" if hybrid
-             else "6-layer distance MLP (3072-5120x5-10)")
-    loss_name = "cross-entropy on worst-case logits, eps_train 0.0345" if hybrid else "hinge loss"
+    model = ("HybridModel(depth=7, width=5120, hidden=512, identity_val=10.0)" if kind == "hybrid"
+             else "MLPModel(depth=6, width=5120, identity_val=10.0)")
+    loss_name = "cross-entropy on worst-case logits, eps_train 0.0345" if kind == "hybrid" else "hinge loss"
     return {"metric": name, "value": round(value, 1), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": ("%s training step, p=%s, %s, SGD lr 0.02, batch %d per rank"
-                                    % (model, args.p, loss_name, B)) if train else
+            "config": {"workload": ("%s training step, p=%s, %s, %s, batch %d per rank"
+                                    % (model, args.p, loss_name, step.optimizer_name, B)) if train else
                                    ("%s certification (value + interval bounds, eps=8/255), p=inf, batch %d per rank"
                                     % (model, B)),
                        "batch_per_rank": B, "l2": "working set 560 MB of weights per step, larger than L2"},
             "e2e": {"value": round(value, 1), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "api": "l_inf_dist_net_v2_b200 modules + autograd + torch.optim.SGD"},
+                    "api": "l_inf_dist_net_v2_b200 models + autograd + parallel.OverlappedDataParallel + optim"},
             "gpu_launches": launches, "clocks": clocks}
 
 
@@ -823,6 +927,10 @@ def run_reference_cuda(args, rank, local_rank):
 
 
 def main():
+    # Libraries (NCCL among them) may print to stdout; the contract is ONE JSON line there.  Everything else that is
+    # written to file descriptor 1 while the benchmark runs goes to stderr.
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     args = parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -837,13 +945,21 @@ def main():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             torch.cuda.set_device(local_rank)
             dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        line = run_ours(args, rank, world, local_rank) if args.workload == "layer" else run_mlp(args, rank, world, local_rank)
+        comm_group = None
+        if world > 1 and args.reserve_sms > 0:
+            from l_inf_dist_net_v2_b200.parallel import nccl_group_with_cta_limit
+            comm_group = nccl_group_with_cta_limit(args.reserve_sms)
+        if args.workload == "layer":
+            line = run_ours(args, rank, world, local_rank, comm_group)
+        else:
+            line = run_model(args, rank, world, local_rank, comm_group)
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
             dist.destroy_process_group()
     if line is not None:
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
 
 
 if __name__ == "__main__":

@@ -84,27 +84,33 @@ def nccl_group_with_cta_limit(max_ctas):
 
 class OverlappedDataParallel:
     """Data-parallel training with DistributedDataParallel's semantics (main.py:357: every rank applies the mean of all
-    ranks' gradients) and the gradient exchange hidden behind the next step's forward pass.
+    ranks' gradients) and most of the gradient exchange hidden behind the next step's forward pass.
 
     At p = inf a layer's backward pass is a scatter of a few hundred microseconds while its weight gradient is
     60-100 MB, so there is no backward work to hide the all-reduce behind.  Instead:
 
-      * each parameter's all-reduce (mean) starts from a gradient hook as soon as that gradient is complete;
-      * `step()` only marks the updates as due; a layer's own optimiser applies its update in a forward pre-hook, just
-        before that layer is used again, after waiting for that layer's all-reduce only.  The last layers' collectives
-        (issued first during backward) thus run beside the first layers' forward kernels of the next step.  The values
-        every layer computes with are exactly those of the usual "all-reduce, then step" order;
-      * while collectives are in flight the persistent distance kernels leave `reserve_sms` SMs free
-        (ldn_set_max_ctas), which is where a CTA-limited NCCL group (nccl_group_with_cta_limit) runs.
+      * `step()` (after backward) starts one all-reduce (mean) per parameter in FORWARD order and marks every layer's
+        update as due; nothing waits;
+      * a layer's own optimiser applies its update in a forward pre-hook, just before that layer is used again, after
+        waiting for that layer's collectives only.  So only the first layer's exchange is exposed; the later layers'
+        run beside the forward kernels of the layers in front of them.  The values every layer computes with are
+        exactly those of the usual "all-reduce everything, then step" order;
+      * the first layer's collectives use `first_group` (default: `group`); the others use `group`, which may be a
+        CTA-limited NCCL group (nccl_group_with_cta_limit): while those are in flight the persistent distance kernels
+        leave `reserve_sms` SMs free (ldn_set_max_ctas) for them -- a kernel that takes every SM would otherwise
+        either keep the collective waiting or lose SMs to it in mid-flight.
 
     `optimizer_factory(params)` builds one optimiser per layer (any torch.optim optimiser, or optim.FusedAdam /
     FusedSGD).  Call `finish()` before evaluating, checkpointing or reading parameters: it applies what is still due
     and, like DistributedDataParallel's buffer broadcast, copies rank 0's buffers (MeanShift running means) to all ranks.
     """
 
-    def __init__(self, model, optimizer_factory, group=None, reserve_sms=0, set_max_ctas=None):
+    SMALL = 4 << 20  # pending bytes below which the distance kernels take all SMs again
+
+    def __init__(self, model, optimizer_factory, group=None, first_group=None, reserve_sms=0, set_max_ctas=None):
         self.model = model
         self.group = group
+        self.first_group = first_group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.reserve_sms = reserve_sms if self.world > 1 else 0
         self._set_max_ctas = set_max_ctas
@@ -112,26 +118,14 @@ class OverlappedDataParallel:
         self._capped = False
         self.units = []
         self.exchange = self.world > 1
-        avg = self.world > 1 and dist.get_backend(group) == "nccl"
         for module in model.modules():
             params = [q for q in module.parameters(recurse=False) if q.requires_grad]
             if not params:
                 continue
             unit = {"module": module, "params": params, "optimizer": optimizer_factory(params), "pending": [],
-                    "due": False}
+                    "bytes": 0, "due": False}
             self.units.append(unit)
             module.register_forward_pre_hook(lambda mod, args, u=unit: self._apply(u))
-            for q in params:
-                q.register_post_accumulate_grad_hook(lambda prm, u=unit, a=avg: self._grad_ready(u, prm, a))
-
-    # -- hooks ----------------------------------------------------------------------------------------------------
-    def _grad_ready(self, unit, prm, avg):
-        if not self.exchange:
-            return
-        op = dist.ReduceOp.AVG if avg else dist.ReduceOp.SUM
-        work = dist.all_reduce(prm.grad, op=op, group=self.group, async_op=True)
-        unit["pending"].append((work, None if avg else prm))
-        self._cap(True)
 
     def _cap(self, on):
         if self.reserve_sms <= 0 or on == self._capped:
@@ -152,18 +146,34 @@ class OverlappedDataParallel:
             if summed is not None:  # backends without an averaging reduction
                 summed.grad.div_(self.world)
         unit["pending"].clear()
+        unit["bytes"] = 0
         unit["optimizer"].step()
         for q in unit["params"]:
             q.grad = None
         unit["due"] = False
-        if self._capped and not any(not w.is_completed() for u in self.units for w, _ in u["pending"]):
+        # kernels launched from here on are ordered behind every collective whose wait is already in the stream
+        if self._capped and sum(u["bytes"] for u in self.units) < self.SMALL:
             self._cap(False)
 
     # -- training-loop interface ------------------------------------------------------------------------------------
     def step(self):
-        """After backward: every layer's update becomes due (applied before the layer's next forward, or by finish())."""
+        """After backward: start the exchange (forward order) and make every layer's update due; the update itself
+        happens before the layer's next forward, or in finish()."""
+        first = True
         for unit in self.units:
+            grads = [q for q in unit["params"] if q.grad is not None]
+            if self.exchange and grads:
+                group = (self.first_group if first and self.first_group is not None else self.group)
+                avg = dist.get_backend(group) == "nccl"
+                op = dist.ReduceOp.AVG if avg else dist.ReduceOp.SUM
+                for q in grads:
+                    work = dist.all_reduce(q.grad, op=op, group=group, async_op=True)
+                    unit["pending"].append((work, None if avg else q))
+                    unit["bytes"] += q.grad.numel() * q.grad.element_size()
+                first = False
             unit["due"] = True
+        if self.exchange and sum(u["bytes"] for u in self.units[1:]) >= self.SMALL:
+            self._cap(True)
 
     def finish(self):
         for unit in self.units:
