@@ -125,6 +125,16 @@ View w_natural_view(const float* w, const Shape& s) {
     return View{w, s.CIg, s.COg, s.G, s.CIg, static_cast<long long>(s.COg) * s.CIg, 1};
 }
 
+// Convolution-shaped inputs x[B, CI, HW] can be read in place as a k-major operand (positions contiguous, channels
+// 32 per stage) when TMA can address them (HW a multiple of 4 floats, 16-byte aligned base) and a 128-position tile
+// is mostly filled; every (sample, group) pair is then its own engine group.  Other shapes take the transposed copy.
+bool x_inplace_kmajor(const float* x, const Shape& s) { return s.HW >= 96 && s.HW % 4 == 0 && aligned16(x); }
+View x_kmajor_view(const float* x, const Shape& s) {
+    return View{x, s.HW, s.CIg, static_cast<long long>(s.B) * s.G, s.HW, static_cast<long long>(s.CIg) * s.HW, 1};
+}
+// tile width (in units of 16 columns) for a layer with `cog` outputs per group
+inline int narrow_reg_n(int cog) { return cog <= 32 ? 2 : (cog <= 64 ? 4 : 8); }
+
 size_t x_scratch_bytes(const float* x, const Shape& s) {
     return x_is_natural(x, s) ? 0 : pad256(canonical_floats(s.CIg, s.M, s.G) * sizeof(float));
 }
@@ -182,28 +192,41 @@ OutAddr w_addr(const Shape& s) {
     return OutAddr{s.CIg, 0, static_cast<long long>(s.COg) * s.CIg, 1, 1};
 }
 
-// forward-type problem: out (m = (b, hw), n = o), k = c
+// forward-type problem: out (m = (b, hw), n = o), k = c.  inplace: a0 is x_kmajor_view (HW > 1 read in place): one
+// engine group per (sample, group), m = hw.
 int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, const View& wv, const Shape& s,
-                float* out0, float* out1, int* outi0, int* outi1, const float* pres, float p) {
+                float* out0, float* out1, int* outi0, int* outi1, const float* pres, float p, bool inplace = false) {
     TileLaunch L;
-    OpGeom geom{kTileN, 1};
-    if (kind == FwdKind::PowInt || kind == FwdKind::PowGen || kind == FwdKind::PowNorm) geom = fwd_pow_geom(kind, ip);
-    else geom = fwd_inf_geom(kind);
-    int r = fill_plan(c, &L, s.M, s.COg, s.CIg, s.G, fwd_acc_arrays(kind), geom);
+    const int rn = fwd_variant_supported(kind, ip) ? narrow_reg_n(s.COg) : 8;
+    const bool variant = inplace || rn != 8;
+    if (inplace && !fwd_variant_supported(kind, ip)) return kBadArgument;
+    OpGeom geom{16 * rn, 1};
+    if (!variant) {
+        if (kind == FwdKind::PowInt || kind == FwdKind::PowGen || kind == FwdKind::PowNorm) geom = fwd_pow_geom(kind, ip);
+        else geom = fwd_inf_geom(kind);
+    }
+    const long long groups = inplace ? static_cast<long long>(s.B) * s.G : s.G;
+    if (groups > 0x7fffffffLL) return kBadArgument;
+    int r = fill_plan(c, &L, inplace ? s.HW : s.M, s.COg, s.CIg, static_cast<int>(groups), fwd_acc_arrays(kind), geom);
     if (r != kOk) return r;
     TileParams& P = L.params;
     P.a_row_coord = a0.row_coord;
     P.b_row_coord = wv.row_coord;
+    P.b_group_mod = inplace ? s.G : 0;
     P.a0 = as_operand(a0);
     P.a1 = a1 ? as_operand(*a1) : P.a0;
     P.b = as_operand(wv);
     P.pres = Operand{pres, 0, 0};
-    P.out = y_addr(s);
+    // y[((b G + g) COg + o) HW + hw]: with one engine group per (b, g) the row index is hw itself
+    P.out = inplace ? OutAddr{1, 0, static_cast<long long>(s.COg) * s.HW, s.HW, 1} : y_addr(s);
     P.out_f0 = out0; P.out_f1 = out1; P.out_i0 = outi0; P.out_i1 = outi1;
     P.p = p; P.q = p - 1.0f;
-    if ((r = build_map(&L.map_a0, a0, Layout::RowMajor)) != kOk) return r;
-    if ((r = build_map(&L.map_a1, a1 ? *a1 : a0, Layout::RowMajor)) != kOk) return r;
+    const Layout la = inplace ? Layout::KMajor : Layout::RowMajor;
+    if ((r = build_map(&L.map_a0, a0, la)) != kOk) return r;
+    if ((r = build_map(&L.map_a1, a1 ? *a1 : a0, la)) != kOk) return r;
     if ((r = build_map(&L.map_b, wv, Layout::RowMajor, geom.tile_n)) != kOk) return r;
+    if (inplace) return launch_fwd_variant_k(kind, rn, L, c.st);
+    if (variant) return launch_fwd_variant_row(kind, rn, L, c.st);
     switch (kind) {
         case FwdKind::PowInt:
         case FwdKind::PowGen:
@@ -348,15 +371,24 @@ int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* p
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
     const FwdKind kind = pos ? FwdKind::InfPos : FwdKind::Inf;
-    size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + partial_bytes(cap_for(ctx), fwd_acc_arrays(kind));
+    const bool inplace = x_inplace_kmajor(x, s);
+    size_t need = (inplace ? 0 : x_scratch_bytes(x, s)) + w_scratch_bytes(w, s) +
+                  partial_bytes(cap_for(ctx), fwd_acc_arrays(kind));
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     View xv, wv;
-    if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
+    if (inplace) xv = x_kmajor_view(x, s);
+    else if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
     if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
-    r = run_forward(c, kind, 0, xv, nullptr, wv, s, y, nullptr, pos, nullptr, nullptr, INFINITY);
+    r = run_forward(c, kind, 0, xv, nullptr, wv, s, y, nullptr, pos, nullptr, nullptr, INFINITY, inplace);
     if (r != kOk || !pos) return r;
-    return launch_rescan(0, as_operand(xv), as_operand(xv), as_operand(wv), y, pos, s, c.st);
+    if (inplace) {
+        // the input as the index search addresses it: element (sample-group bg, position hw, channel k) at
+        // bg * stride_group + hw * stride_row + k * HW
+        const Operand xin{x, 1, static_cast<long long>(s.CIg) * s.HW};
+        return launch_rescan(0, xin, xin, as_operand(wv), y, pos, s, c.st, s.HW);
+    }
+    return launch_rescan(0, as_operand(xv), as_operand(xv), as_operand(wv), y, pos, s, c.st, 1);
 }
 
 int bound_forward(const float* xl, const float* xu, const float* w, const Shape& s, float* yl, float* yu, int* pl,
@@ -382,15 +414,15 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
         // one pass: both bounds and the stage of each extremum, then the two index searches
         r = run_forward(c, FwdKind::BoundPosBoth, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
         if (r != kOk) return r;
-        if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st)) != kOk) return r;
-        return launch_rescan(2, as_operand(lv), as_operand(uv), as_operand(wv), yu, pu, s, c.st);
+        if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st, 1)) != kOk) return r;
+        return launch_rescan(2, as_operand(lv), as_operand(uv), as_operand(wv), yu, pu, s, c.st, 1);
     }
     r = run_forward(c, FwdKind::BoundPosLower, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
     if (r != kOk) return r;
-    if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st)) != kOk) return r;
+    if ((r = launch_rescan(1, as_operand(lv), as_operand(uv), as_operand(wv), yl, pl, s, c.st, 1)) != kOk) return r;
     r = run_forward(c, FwdKind::BoundPosUpper, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
     if (r != kOk) return r;
-    return launch_rescan(2, as_operand(lv), as_operand(uv), as_operand(wv), yu, pu, s, c.st);
+    return launch_rescan(2, as_operand(lv), as_operand(uv), as_operand(wv), yu, pu, s, c.st, 1);
 }
 
 }  // namespace
@@ -461,24 +493,26 @@ LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B
     const DeviceCtx* ctx;
     if ((r = get_device_ctx(&ctx)) != kOk) return r;
     const bool normalised = p > 10.0f;  // MIN_NORMALIZED_P of the reference
+    const int ip = normalised ? -1 : int_power(p);
+    const FwdKind kind = normalised ? FwdKind::PowNorm : (ip >= 1 ? FwdKind::PowInt : FwdKind::PowGen);
+    const bool inplace = x_inplace_kmajor(input, s) && fwd_variant_supported(kind, ip);
     const size_t ybytes = pad256(sizeof(float) * static_cast<size_t>(B) * CO * HW);
-    size_t need = x_scratch_bytes(input, s) + w_scratch_bytes(weight, s) + 2 * partial_bytes(cap_for(ctx), 1) +
-                  (normalised ? ybytes : 0);
+    size_t need = (inplace ? 0 : x_scratch_bytes(input, s)) + w_scratch_bytes(weight, s) +
+                  2 * partial_bytes(cap_for(ctx), 1) + (normalised ? ybytes : 0);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     View xv, wv;
-    if ((r = get_x_view(c, input, s, &xv)) != kOk) return r;
+    if (inplace) xv = x_kmajor_view(input, s);
+    else if ((r = get_x_view(c, input, s, &xv)) != kOk) return r;
     if ((r = get_w_view(c, weight, s, &wv)) != kOk) return r;
-    if (!normalised) {
-        const int ip = int_power(p);
-        if (ip >= 1) return run_forward(c, FwdKind::PowInt, ip, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, p);
-        return run_forward(c, FwdKind::PowGen, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, p);
-    }
+    if (!normalised)
+        return run_forward(c, kind, ip >= 1 ? ip : -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, p,
+                           inplace);
     float* mbuf = c.bump.take<float>(static_cast<size_t>(B) * CO * HW);
     if (!mbuf) return kWorkspace;
-    r = run_forward(c, FwdKind::Inf, 0, xv, nullptr, wv, s, mbuf, nullptr, nullptr, nullptr, nullptr, INFINITY);
+    r = run_forward(c, FwdKind::Inf, 0, xv, nullptr, wv, s, mbuf, nullptr, nullptr, nullptr, nullptr, INFINITY, inplace);
     if (r != kOk) return r;
-    return run_forward(c, FwdKind::PowNorm, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, mbuf, p);
+    return run_forward(c, FwdKind::PowNorm, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, mbuf, p, inplace);
 }
 
 LDN_API int ldn_norm_dist_forward_with_max(const float* input, const float* weight, const float* max_output,

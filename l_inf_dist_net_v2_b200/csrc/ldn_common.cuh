@@ -62,6 +62,7 @@ struct TileParams {
     long long total_iters;      // G * tiles_m * tiles_n * kt
     int a_row_coord;            // which TMA coordinate (1 or 2) is the row/k index of A; the other is g
     int b_row_coord;            // same for B
+    int b_group_mod;            // > 0: B's group coordinate is (engine group) % b_group_mod; 0: the engine group
     Operand a0, a1, b, pres;    // generic views (rescan of argmax chunks, resident per-output operand)
     OutAddr out;
     float* out_f0;

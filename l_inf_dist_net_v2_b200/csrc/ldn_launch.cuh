@@ -35,6 +35,15 @@ OpGeom bwd_fused_geom(int iq);
 OpGeom bwd_x_geom(int iq);
 OpGeom bwd_w_geom(int iq);
 
+// Forward ops that also exist with a k-major A operand (inputs with HW > 1 read in place) and with 64- / 32-wide
+// tiles: PowInt with ip == 8, PowGen, PowNorm, Inf, InfPos.  reg_n = 8, 4 or 2 (tile width 16 * reg_n).
+inline bool fwd_variant_supported(FwdKind kind, int ip) {
+    return (kind == FwdKind::PowInt && ip == 8) || kind == FwdKind::PowGen || kind == FwdKind::PowNorm ||
+           kind == FwdKind::Inf || kind == FwdKind::InfPos;
+}
+int launch_fwd_variant_row(FwdKind kind, int reg_n, const TileLaunch& L, cudaStream_t st);  // row-major A, reg_n 4 or 2
+int launch_fwd_variant_k(FwdKind kind, int reg_n, const TileLaunch& L, cudaStream_t st);    // k-major A, reg_n 8, 4, 2
+
 int launch_fwd_pow(FwdKind kind, int ip, const TileLaunch& L, cudaStream_t st);   // PowInt (ip 1..8), PowGen, PowNorm
 int launch_fwd_inf(FwdKind kind, const TileLaunch& L, cudaStream_t st);           // Inf, InfPos, Bound, BoundPos{Lower,Upper,Both}
 // iq 0..8: integer p - 1; -1: general p with 1/y folded into the exponent offset; -2: general p, unfolded

@@ -199,6 +199,16 @@ struct FwdLayout {
     static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
 };
 
+// A forward op with another A layout and / or a narrower tile: LA_ = KMajor reads convolution-shaped inputs
+// x[B, C, HW] in place (HW contiguous: tiles of [32 channels][128 positions], every sample its own engine group);
+// RN_ = 4 / 2 are the 128 x 64 / 128 x 32 tiles for layers with few outputs per group.
+template <class Base, Layout LA_, int RN_>
+struct FwdVariant : Base {
+    static constexpr Layout LA = LA_;
+    static constexpr int REG_N = RN_;
+    static constexpr int CTAS_PER_SM = 1;
+};
+
 // ------------------------------------------------------------------------------------------------
 // Finite p, forward
 // ------------------------------------------------------------------------------------------------

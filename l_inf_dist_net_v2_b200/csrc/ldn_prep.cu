@@ -162,7 +162,7 @@ __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __res
 // per output is one division by HW (none for fully connected layers) and, for those, a block keeps rereading one
 // input row, which stays in the L1 cache: only the weight pieces come from L2.
 __global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const float* __restrict__ y,
-                              int* __restrict__ pos, Shape s) {
+                              int* __restrict__ pos, Shape s, long long a_stride_k) {
     const int kpad = (s.CIg + 3) & ~3;
     const int q = threadIdx.x & 7;
     const int group_in_block = threadIdx.x >> 3;
@@ -186,7 +186,17 @@ __global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const
                 const long long m = static_cast<long long>(bi) * s.HW + hw;
                 const int k = stage * 32 + 4 * q;
                 if (k < kpad) {
-                    const float4 av = *reinterpret_cast<const float4*>(arow + m * a0.stride_row + k);
+                    float4 av;
+                    if (a_stride_k == 1) {
+                        av = *reinterpret_cast<const float4*>(arow + m * a0.stride_row + k);
+                    } else {
+                        // input read in place (channels HW apart, no padding behind the last one)
+                        const float* ap = a0.ptr + bg * a0.stride_group + hw * a0.stride_row + k * a_stride_k;
+                        av.x = ap[0];
+                        av.y = k + 1 < s.CIg ? ap[a_stride_k] : 0.0f;
+                        av.z = k + 2 < s.CIg ? ap[2 * a_stride_k] : 0.0f;
+                        av.w = k + 3 < s.CIg ? ap[3 * a_stride_k] : 0.0f;
+                    }
                     const float4 bv = *reinterpret_cast<const float4*>(brow + o * b.stride_row + k);
                     float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (mode != 0) uv = *reinterpret_cast<const float4*>(urow + m * a1.stride_row + k);
@@ -346,14 +356,15 @@ int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, co
 }
 
 int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, int* pos, const Shape& s,
-                  cudaStream_t st) {
+                  cudaStream_t st, long long a_stride_k) {
+    if (a_stride_k != 1 && mode != 0) return kBadArgument;
     const long long cohw = static_cast<long long>(s.COg) * s.HW;
     const long long bg = static_cast<long long>(s.B) * s.G;
     if (cohw > 0x7fffffffLL || bg > 0x7fffffffLL) return kBadArgument;
     long long chunks = (cohw + kRescanChunk - 1) / kRescanChunk;
     if (chunks > 65535) chunks = 65535;  // the kernel strides over the rest
     rescan_kernel<<<dim3(static_cast<unsigned>(bg), static_cast<unsigned>(chunks)), kBlock, 0, st>>>(mode, a0, a1, b, y,
-                                                                                                      pos, s);
+                                                                                                      pos, s, a_stride_k);
     LDN_LAUNCH_RET();
 }
 

@@ -31,9 +31,11 @@ int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, co
 //   mode 0: p = inf value y = max |a - b|, flag = (a - b < 0)          (a1 unused; none: 0)
 //   mode 1: lower bound, y = -min(min(t1, t2)),  t1 = b - a0, t2 = a1 - b, flag = (t1 > t2)   (none: 0xffffffff)
 //   mode 2: upper bound, y = max(max(t1, t2)), same flag                (none: 0)
-// Operands are given as generic views (row / group strides in elements, reduction index contiguous).
+// Operands are given as generic views (row / group strides in elements, reduction index contiguous).  With
+// a_stride_k != 1 (mode 0 only) a0 is an input read in place: element (sample-group bg, position hw, channel k) at
+// a0.ptr + bg * a0.stride_group + hw * a0.stride_row + k * a_stride_k.
 int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, int* pos, const Shape& s,
-                  cudaStream_t st);
+                  cudaStream_t st, long long a_stride_k);
 
 // grad_weight of the fused backward: gw[i] = -sum_t part[t * count + i], t < tiles
 int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, cudaStream_t st);

@@ -25,10 +25,12 @@ enum class Layout { RowMajor, KMajor };
 
 constexpr int kStages = 4;  // default depth of the operand ring (Op::STAGES)
 
-// R = number of rows / columns a thread owns in that dimension (8, or 4 for the narrow 128 x 64 tile)
+// R = number of rows / columns a thread owns in that dimension (8; 4 or 2 for the narrow 128 x 64 / 128 x 32 tiles,
+// the latter with row-major operands only)
 template <Layout L, int R = 8>
 __device__ __forceinline__ int own_index(int t, int r) {
     if (L == Layout::RowMajor) return t + 16 * r;
+    static_assert(L == Layout::RowMajor || R == 8 || R == 4, "a k-major tile is 128 or 64 columns wide");
     if (R == 4) return t * 4 + r;
     return (r >> 2) * 64 + t * 4 + (r & 3);
 }
@@ -37,7 +39,8 @@ __device__ __forceinline__ int own_index(int t, int r) {
 // tile for k-group `ps` (k = ps * KS .. ps * KS + KS - 1 inside the 32-wide stage).
 template <Layout L, int KS, int R>
 __device__ __forceinline__ void fetch_slab(const char* tile, int t, int ps, float (&v)[R][KS]) {
-    static_assert(R == 8 || R == 4, "a thread owns 8 or 4 rows / columns");
+    static_assert(R == 8 || R == 4 || R == 2, "a thread owns 8, 4 or 2 rows / columns");
+    static_assert(L == Layout::RowMajor || R != 2, "a k-major tile is 128 or 64 columns wide");
     static_assert(KS == 1 || KS == 2 || KS == 4, "k-step must be 1, 2 or 4");
     if (L == Layout::RowMajor) {
         const int k = ps * KS;
@@ -135,7 +138,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     constexpr int RN = Op::REG_N;          // output columns per thread
     constexpr int TN = 16 * RN;            // output columns per tile
     constexpr int TELEMS = kTileM * TN;    // outputs per tile
-    static_assert(RN == 8 || RN == 4, "a thread owns 8 or 4 output columns");
+    static_assert(RN == 8 || RN == 4 || RN == 2, "a thread owns 8, 4 or 2 output columns");
 
     extern __shared__ char smem_raw[];
     char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -184,7 +187,8 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
         {
             int c0, c1, c2;
             if (Op::LB == Layout::RowMajor) { c0 = k0; c1 = tc.n0; } else { c0 = tc.n0; c1 = k0; }
-            c2 = tc.g;
+            // (when every sample is its own engine group, B -- the weight -- still has only the layer's groups)
+            c2 = P.b_group_mod > 0 ? tc.g % P.b_group_mod : tc.g;
             if (P.b_row_coord == 2) { int t = c1; c1 = c2; c2 = t; }
             tma_load_3d(st + NA * kOperandTileBytes, &map_b, bar, c0, c1, c2);
         }

@@ -166,6 +166,12 @@ SHAPES = [
     (5, 48, 264, 1, 49),
     (300, 260, 10, 1, 1),
     (4, 70, 24, 2, 64),
+    # HW >= 96 and a multiple of 4: the input is read in place (k-major operand, one engine group per sample);
+    # few outputs per group: 64- and 32-wide tiles
+    (3, 40, 24, 2, 100),
+    (2, 70, 80, 1, 128),
+    (4, 36, 48, 1, 196),
+    (2, 33, 130, 1, 260),
 ]
 
 
