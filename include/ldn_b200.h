@@ -232,6 +232,24 @@ LDN_API int ldn_bound_inf_dist_backward_input_weight(const float* grad_outputL, 
                                              int HW, float* grad_inputL, float* grad_inputU, float* grad_weight,
                                              ldn_stream_t stream);
 
+/* ---- eval-mode layer in one kernel -------------------------------------------------------------- */
+
+/*
+ * ldn_inf_dist_forward_nograd / ldn_bound_inf_dist_forward_nograd with the rest of an eval-mode layer folded into
+ * the store (no counterpart in the reference, which runs them as separate elementwise passes,
+ * core/modules/basic_modules.py:128-132 and core/modules/norm_dist.py:37-38): every stored value is
+ *     (y - sub[o]) + add[o],   o = output channel in 0..CO-1,
+ * with the same two roundings as the separate passes; sub (the MeanShift running mean) and add (the layer bias) are
+ * device arrays of CO floats, either may be NULL.
+ */
+LDN_API int ldn_inf_dist_forward_nograd_shifted(const float* input, const float* weight, int B, int CO, int CI, int G,
+                                                int HW, float* output, const float* sub, const float* add,
+                                                ldn_stream_t stream);
+LDN_API int ldn_bound_inf_dist_forward_nograd_shifted(const float* inputL, const float* inputU, const float* weight,
+                                                      int B, int CO, int CI, int G, int HW, float* outputL,
+                                                      float* outputU, const float* sub, const float* add,
+                                                      ldn_stream_t stream);
+
 /* ---- allocation-free variant ------------------------------------------------------------------ */
 
 /*

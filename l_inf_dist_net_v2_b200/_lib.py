@@ -31,6 +31,8 @@ SIGNATURES = {
                                          [_c_float_p, _c_float_p, _s],
     "ldn_bound_inf_dist_backward_input_weight": [_c_float_p, _c_float_p, _c_int_p, _c_int_p] + [_i] * 5 +
                                                 [_c_float_p, _c_float_p, _c_float_p, _s],
+    "ldn_inf_dist_forward_nograd_shifted": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _c_float_p, _c_float_p, _s],
+    "ldn_bound_inf_dist_forward_nograd_shifted": [_c_float_p] * 3 + [_i] * 5 + [_c_float_p] * 4 + [_s],
     "ldn_inf_dist_forward_nograd_noalloc": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _s],
     "ldn_mean_shift_rows": [_c_float_p, _i, _i, _c_float_p, _f, _c_float_p, _c_float_p, _s],
     "ldn_adam_update": [_i, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,

@@ -90,6 +90,8 @@ struct Call {
     Bump bump;
     cudaStream_t st;
     int cap;  // persistent CTAs
+    const float* col_sub = nullptr;  // epilogue of the no-grad p = inf kernels (see TileParams)
+    const float* col_add = nullptr;
     std::unique_lock<std::mutex> lock;  // the arena's call mutex, released when the entry point returns
 };
 
@@ -221,6 +223,10 @@ int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, c
     P.out = inplace ? OutAddr{1, 0, static_cast<long long>(s.COg) * s.HW, s.HW, 1} : y_addr(s);
     P.out_f0 = out0; P.out_f1 = out1; P.out_i0 = outi0; P.out_i1 = outi1;
     P.p = p; P.q = p - 1.0f;
+    if (kind == FwdKind::Inf || kind == FwdKind::Bound) {
+        P.col_sub = c.col_sub;
+        P.col_add = c.col_add;
+    }
     const Layout la = inplace ? Layout::KMajor : Layout::RowMajor;
     if ((r = build_map(&L.map_a0, a0, la)) != kOk) return r;
     if ((r = build_map(&L.map_a1, a1 ? *a1 : a0, la)) != kOk) return r;
@@ -365,7 +371,8 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
     return norm_dist_backward_part(go, x, w, y, s, gx, gw, p, stream, false);
 }
 
-int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* pos, ldn_stream_t stream) {
+int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* pos, ldn_stream_t stream,
+                const float* col_sub = nullptr, const float* col_add = nullptr) {
     if (!x || !w || !y) return kBadArgument;
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
@@ -376,6 +383,8 @@ int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* p
                   partial_bytes(cap_for(ctx), fwd_acc_arrays(kind));
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    c.col_sub = col_sub;
+    c.col_add = col_add;
     View xv, wv;
     if (inplace) xv = x_kmajor_view(x, s);
     else if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
@@ -392,7 +401,7 @@ int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* p
 }
 
 int bound_forward(const float* xl, const float* xu, const float* w, const Shape& s, float* yl, float* yu, int* pl,
-                  int* pu, ldn_stream_t stream) {
+                  int* pu, ldn_stream_t stream, const float* col_sub = nullptr, const float* col_add = nullptr) {
     if (!xl || !xu || !w || !yl || !yu || ((pl == nullptr) != (pu == nullptr))) return kBadArgument;
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
@@ -401,6 +410,8 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
     size_t need = 2 * pad256(xfloats * sizeof(float)) + w_scratch_bytes(w, s) + 2 * partial_bytes(cap_for(ctx), 5);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
+    c.col_sub = col_sub;
+    c.col_add = col_add;
     float* lc = c.bump.take<float>(xfloats);
     float* uc = c.bump.take<float>(xfloats);
     if (!lc || !uc) return kWorkspace;
@@ -564,6 +575,27 @@ LDN_API int ldn_inf_dist_forward_nograd(const float* input, const float* weight,
     if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
     if (r != kOk) return r;
     return inf_forward(input, weight, s, output, nullptr, stream);
+}
+
+LDN_API int ldn_inf_dist_forward_nograd_shifted(const float* input, const float* weight, int B, int CO, int CI, int G,
+                                                int HW, float* output, const float* sub, const float* add,
+                                                ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
+    if (r != kOk) return r;
+    return inf_forward(input, weight, s, output, nullptr, stream, sub, add);
+}
+
+LDN_API int ldn_bound_inf_dist_forward_nograd_shifted(const float* inputL, const float* inputU, const float* weight,
+                                                      int B, int CO, int CI, int G, int HW, float* outputL,
+                                                      float* outputU, const float* sub, const float* add,
+                                                      ldn_stream_t stream) {
+    Shape s;
+    int r = check_shape(B, CO, CI, G, HW, &s);
+    if (r == kEmptyBatch) return empty_result(nullptr, CO, CI, G, stream);
+    if (r != kOk) return r;
+    return bound_forward(inputL, inputU, weight, s, outputL, outputU, nullptr, nullptr, stream, sub, add);
 }
 
 LDN_API int ldn_inf_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,

@@ -71,6 +71,8 @@ struct TileParams {
     int* out_i1;
     float p;                    // the exponent the op was called with
     float q;                    // op specific (p - 1 for backward)
+    const float* col_sub;       // optional per-output-channel epilogue of the no-grad p = inf kernels:
+    const float* col_add;       //   stored value = (result - col_sub[channel]) + col_add[channel]; either may be null
     float* side_out;            // fused backward: per-row-tile column sums [tile_m][g][k][n] (else null)
     float* partials;            // stream-K scratch: [grid][2][arrays][kTileElems]
     int* status;                // device status word (0 = ok)

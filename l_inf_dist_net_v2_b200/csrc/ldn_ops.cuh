@@ -328,6 +328,17 @@ struct FwdPowNorm : FwdLayout {
 // first channel equal to the maximum, which is the index a strictly-greater scan in ascending channel
 // order ends with.
 // ------------------------------------------------------------------------------------------------
+// Epilogue of the no-grad p = inf kernels: subtract the layer's running mean, add its bias (the two elementwise
+// passes of an eval-mode layer, core/modules/basic_modules.py:128-132 and core/modules/norm_dist.py:37-38, with the
+// same two roundings).  Channel = layer group * outputs per group + n.
+__device__ __forceinline__ float col_epilogue(float v, int n, int g, const TileParams& P) {
+    if (P.col_sub == nullptr && P.col_add == nullptr) return v;
+    const int ch = (P.b_group_mod > 0 ? g % P.b_group_mod : g) * P.N + n;
+    if (P.col_sub) v = __fsub_rn(v, P.col_sub[ch]);
+    if (P.col_add) v = __fadd_rn(v, P.col_add[ch]);
+    return v;
+}
+
 template <bool POS>
 struct FwdInf : FwdLayout {
     static constexpr bool N_IN_SMEM = POS;  // frees 64 registers of the indexed kernel (0.83 -> 0.79 ms)
@@ -384,7 +395,7 @@ struct FwdInf : FwdLayout {
     __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
     __device__ static void finalize(const float* f, const int* nn, float, int m, int n, int g, const TileParams& P) {
         const long long off = out_offset(P.out, m, n, g);
-        P.out_f0[off] = f[0];
+        P.out_f0[off] = POS ? f[0] : col_epilogue(f[0], n, g, P);
         if (POS) P.out_i0[off] = nn[0];  // stage id (or -1); turned into the index by rescan_kernel
     }
 };
@@ -428,8 +439,8 @@ struct FwdBound : FwdLayout {
     __device__ static float load_pres(const TileParams&, int, int, int) { return 0.0f; }
     __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
         const long long off = out_offset(P.out, m, n, g);
-        P.out_f0[off] = -f[0];
-        P.out_f1[off] = f[1];
+        P.out_f0[off] = col_epilogue(-f[0], n, g, P);
+        P.out_f1[off] = col_epilogue(f[1], n, g, P);
     }
 };
 

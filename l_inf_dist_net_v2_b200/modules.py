@@ -88,13 +88,44 @@ class NormDistBase(nn.Module):
         self.p = p
         self.mean_shift = MeanShift(out_channels=out_features, affine=False) if mean_shift else None
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self.fused_eval = True  # eval-mode p = inf layers run as one kernel per tensor (False: the separate steps)
         if not hasattr(NormDistBase, "tag"):
             NormDistBase.tag = 0
         NormDistBase.tag += 1
         self.tag = NormDistBase.tag
 
+    def _eval_layer_fused(self, x, lower, upper):
+        """Eval mode, p = inf, nothing needs a gradient: distance (and bounds), running-mean subtraction and bias as
+        one kernel each -- the same values, bit for bit, as the separate steps below."""
+        sub = self.mean_shift.running_mean if self.mean_shift is not None else None
+        if self.mean_shift is not None and self.mean_shift.bias is not None:
+            sub = sub - self.mean_shift.bias
+        add = self.bias
+        out = [None, None, None]
+        if x is not None:
+            out[0] = torch.empty(x.size(0), self.weight.size(0), x.size(2), device=x.device, dtype=torch.float32)
+            _C.inf_dist_forward_nograd_shifted(x, self.weight, out[0], sub, add, self.groups)
+        if lower is not None and upper is not None:
+            out[1] = torch.empty(lower.size(0), self.weight.size(0), lower.size(2), device=lower.device,
+                                 dtype=torch.float32)
+            out[2] = torch.empty_like(out[1])
+            _C.bound_inf_dist_forward_nograd_shifted(lower, upper, self.weight, out[1], out[2], sub, add, self.groups)
+        return out
+
+    def _can_fuse_eval(self, x, lower, upper):
+        if self.training or not self.fused_eval or not math.isinf(self.p):
+            return False
+        tensors = [t for t in (x, lower, upper) if t is not None]
+        if (lower is None) != (upper is None) or not tensors:
+            return False
+        grad = torch.is_grad_enabled() and (self.weight.requires_grad or any(t.requires_grad for t in tensors))
+        return not grad and all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.dim() == 3
+                                for t in tensors)
+
     # x, lower and upper are 3-D tensors of shape (B, C, H*W)
     def forward(self, x=None, lower=None, upper=None):
+        if self._can_fuse_eval(x, lower, upper):
+            return self._eval_layer_fused(x, lower, upper)
         if x is not None:
             x = norm_dist(x, self.weight, self.p, self.groups, tag=self.tag)
         if lower is not None and upper is not None:

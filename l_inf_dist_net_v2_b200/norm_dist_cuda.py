@@ -161,6 +161,31 @@ def mean_shift_rows(x, running_mean, momentum, out):
         check(lib.ldn_mean_shift_rows(a, B, C, rm, float(momentum), y, None, _stream()), "mean_shift_rows")
 
 
+def inf_dist_forward_nograd_shifted(input, weight, output, sub, add, G):
+    """Not part of the reference's extension module: inf_dist_forward_nograd with (y - sub[o]) + add[o] applied in the
+    store; sub / add are (CO,) tensors or None."""
+    a, w, y = _f(input, "input"), _f(weight, "weight"), _f(output, "output")
+    sp = None if sub is None else _f(sub, "sub")
+    ap = None if add is None else _f(add, "add")
+    B, CO, CI, HW = input.size(0), output.size(1), input.size(1), input.size(2)
+    with torch.cuda.device(input.device):
+        check(lib.ldn_inf_dist_forward_nograd_shifted(a, w, B, CO, CI, G, HW, y, sp, ap, _stream()),
+              "inf_dist_forward_nograd_shifted")
+
+
+def bound_inf_dist_forward_nograd_shifted(inputL, inputU, weight, outputL, outputU, sub, add, G):
+    """Not part of the reference's extension module: bound_inf_dist_forward_nograd with the same epilogue on both
+    bounds."""
+    xl, xu, w = _f(inputL, "inputL"), _f(inputU, "inputU"), _f(weight, "weight")
+    yl, yu = _f(outputL, "outputL"), _f(outputU, "outputU")
+    sp = None if sub is None else _f(sub, "sub")
+    ap = None if add is None else _f(add, "add")
+    B, CO, CI, HW = inputL.size(0), outputL.size(1), inputL.size(1), inputL.size(2)
+    with torch.cuda.device(inputL.device):
+        check(lib.ldn_bound_inf_dist_forward_nograd_shifted(xl, xu, w, B, CO, CI, G, HW, yl, yu, sp, ap, _stream()),
+              "bound_inf_dist_forward_nograd_shifted")
+
+
 def check_status():
     """Waits for the current stream and raises if a kernel reported a bounded-wait timeout."""
     check(lib.ldn_check_status(_stream()), "device status check")

@@ -90,10 +90,11 @@ def test_graph_stays_valid_when_scratch_grows_later_and_growth_is_refused_during
     with torch.cuda.graph(graph, stream=s):
         small(x, w, y)
     expected = y.clone()
-    # a much larger call on the same stream: the arena has to grow (conv-shaped input -> canonical copy of 24 MB)
-    xb = torch.rand(64, 96, 1024, device="cuda")
+    # a much larger call on the same stream: the arena has to grow (conv-shaped input whose HW is no multiple of 4
+    # cannot be read in place -> canonical copy of 24 MB)
+    xb = torch.rand(64, 96, 1022, device="cuda")
     wb = torch.randn(32, 96, device="cuda")
-    yb = torch.empty(64, 32, 1024, device="cuda")
+    yb = torch.empty(64, 32, 1022, device="cuda")
     with torch.cuda.stream(s):
         C.inf_dist_forward_nograd(xb, wb, yb, 1)
         # churn the allocator so that a freed block would be reused and overwritten

@@ -652,3 +652,35 @@ def test_fused_mean_shift_matches_torch_operators(C):
         for a, b in zip(fused(x1.detach(), lo, up), plain(x2.detach(), lo, up)):
             assert torch.allclose(a, b, rtol=0, atol=1e-6)
     C.check_status()
+
+
+@pytest.mark.parametrize("shape", [(130, 200, 150, 1, 1), (6, 36, 20, 2, 5), (3, 40, 24, 2, 100), (64, 784, 1024, 1, 1)])
+def test_eval_layer_in_one_kernel_matches_the_separate_steps(C, shape):
+    """Eval-mode p = inf layer: distance / bounds, running-mean subtraction and bias folded into the store must give
+    the bits of the unfused module (distance kernel, then two torch elementwise passes)."""
+    import l_inf_dist_net_v2_b200 as ldn
+    from l_inf_dist_net_v2_b200._lib import lib
+    B, CI, CO, G, HW = shape
+    torch.manual_seed(4)
+    for mean_shift, bias in ((True, True), (True, False), (False, True)):
+        layer = ldn.NormDistBase(CI, CO, groups=G, bias=bias, mean_shift=mean_shift).cuda().eval()
+        with torch.no_grad():
+            if mean_shift:
+                layer.mean_shift.running_mean.copy_(torch.randn(CO) * 3)
+            if bias:
+                layer.bias.copy_(torch.randn(CO))
+        x = torch.rand(B, CI, HW, device="cuda")
+        lo, up = (x - 0.03).clamp(0, 1), (x + 0.03).clamp(0, 1)
+        for max_ctas in (0, 5):
+            lib.ldn_set_max_ctas(max_ctas)
+            with torch.no_grad():
+                layer.fused_eval = True
+                fused = layer(x, lo, up)
+                fused_x_only = layer(x)[0]
+                layer.fused_eval = False
+                plain = layer(x, lo, up)
+            for a, b in zip(fused, plain):
+                assert torch.equal(a, b), (shape, mean_shift, bias, max_ctas)
+            assert torch.equal(fused_x_only, plain[0])
+        lib.ldn_set_max_ctas(0)
+    C.check_status()
