@@ -254,6 +254,13 @@ int int_power(float e) {
 
 // One backward call on rows [0, s.B) of the given pointers.  accumulate_gw: add to grad_weight instead of
 // overwriting it (only the fused path supports that; it is how the row chunks of one call combine).
+//
+// Integer p - 1 = q: the kernels multiply the per-(b, o) coefficient g / y^q by sgn(t) |t|^q, one instruction per
+// pair fewer than the reference's g (|t| / y)^q (norm_dist_cuda.cu:238-243) but with less range: y^-q overflows or
+// |t|^q goes denormal for very small outputs, the coefficient vanishes for very large ones.  The coefficient kernel
+// therefore raises a device flag when some y^-q leaves [1e-30, 1e24], and the same gradients are then recomputed in
+// the normalised form 2^(q lg2(|t| / y)) by the general-p kernels, launched behind the fast ones with that flag as a
+// gate (they return at once when it is clear, which is always for networks' usual value ranges).
 int norm_dist_backward_part(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
                             float* gw, float p, ldn_stream_t stream, bool accumulate_gw) {
     const DeviceCtx* ctx;
@@ -263,11 +270,13 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
     int iq = int_power(p - 1.0f);
     // general p: fold 1 / y into the exponent offset while q lg2|t| keeps the terms accurate to ~1e-5
     if (iq < 0 && p - 1.0f > kFoldMaxQ) iq = -2;
-    const int ncoef = iq >= 0 ? 1 : 2;
-    // general p: coefficient arrays padded to whole tiles (see launch_coef_gen)
-    const long long coef_rows = iq >= 0 ? s.M : (s.M + kTileM - 1) / kTileM * kTileM;
-    const long long coef_pitch = iq >= 0 ? ceil4(s.COg) : (s.COg + kTileK - 1) / kTileK * kTileK;
-    const size_t coef_floats = static_cast<size_t>(coef_pitch) * coef_rows * s.G;
+    const bool guarded = iq >= 1;  // integer form with a range guard (q = 0: the coefficient is g itself)
+    // general p (and the guard's second form): coefficient arrays padded to whole tiles (see launch_coef_gen)
+    const long long gen_rows = (s.M + kTileM - 1) / kTileM * kTileM;
+    const long long gen_pitch = (s.COg + kTileK - 1) / kTileK * kTileK;
+    const size_t gen_floats = static_cast<size_t>(gen_pitch) * gen_rows * s.G;
+    const long long int_pitch = ceil4(s.COg);
+    const size_t int_floats = static_cast<size_t>(int_pitch) * s.M * s.G;
     // Both gradients wanted: one fused kernel evaluates every term once (grad_input accumulators plus
     // per-row-tile column sums for grad_weight).  It needs tiles_m copies of grad_weight as scratch, so very
     // tall problems (conv layouts with many rows) keep the two-kernel path; so does p = 1 (constant terms).
@@ -275,73 +284,110 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
     const size_t side_floats = static_cast<size_t>(tiles_m) * s.CO * s.CIg;
     const bool fused = gx && gw && iq != 0 && side_floats * sizeof(float) <= g_side_limit;
     if (accumulate_gw && !fused) return kBadArgument;
-    size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + ncoef * pad256(coef_floats * sizeof(float)) +
-                  2 * partial_bytes(cap, 1) + (fused ? pad256(side_floats * sizeof(float)) : 0);
+    size_t need = x_scratch_bytes(x, s) + w_scratch_bytes(w, s) + (iq >= 0 ? pad256(int_floats * sizeof(float)) : 0) +
+                  ((iq < 0 || guarded) ? 2 * pad256(gen_floats * sizeof(float)) : 0) +
+                  (guarded ? 4 : 2) * partial_bytes(cap, 1) + (fused ? pad256(side_floats * sizeof(float)) : 0);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     View xv, wv;
     if ((r = get_x_view(c, x, s, &xv)) != kOk) return r;
     if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
-    float* c0 = c.bump.take<float>(coef_floats);
-    float* c1 = ncoef == 2 ? c.bump.take<float>(coef_floats) : nullptr;
-    if (!c0 || (ncoef == 2 && !c1)) return kWorkspace;
-    const long long coef_inner = iq >= 0 ? s.COg : coef_pitch;
-    const View cv0 = View{c0, coef_inner, coef_rows, s.G, coef_pitch, coef_rows * coef_pitch, 1};
-    const View cv1 = View{c1 ? c1 : c0, coef_inner, coef_rows, s.G, coef_pitch, coef_rows * coef_pitch, 1};
-    if (iq >= 0) r = launch_coef_int(go, y, c0, s, static_cast<int>(coef_pitch), iq, c.st);
-    else r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(coef_pitch), coef_rows, p - 1.0f, iq == -1, c.st);
-    if (r != kOk) return r;
+    float* side = nullptr;
+    if (fused && !(side = c.bump.take<float>(side_floats))) return kWorkspace;
+    // the guard's flag: two words of the arena's status block used in turn, each call clears the next call's
+    int* flag = nullptr;
+    int* flag_next = nullptr;
+    if (guarded) {
+        const unsigned turn = c.arena->range_calls++ & 1u;
+        flag = c.arena->status + 1 + turn;
+        flag_next = c.arena->status + 1 + (turn ^ 1u);
+    }
 
-    // grad_input-shaped problem (also the fused kernel's): out (m = (b, hw), n = c), k = o
-    auto plan_rows = [&](TileLaunch& L, const OpGeom geom) -> int {
-        int e = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom);
-        if (e != kOk) return e;
-        TileParams& P = L.params;
-        P.a_row_coord = cv0.row_coord;
-        P.b_row_coord = wv.row_coord;
-        P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(wv);
-        P.pres = as_operand(xv);
-        P.out = x_addr(s);
-        P.out_f0 = gx;
-        P.p = p; P.q = p - 1.0f;
-        if ((e = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return e;
-        if ((e = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return e;
-        return build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n);
+    // the kernels of one arithmetic form (fam: 0..8 integer q, -1 / -2 general p) on coefficient views cv0 / cv1.
+    // gate: run only if *gate != 0 (the guard's second form); the weight-gradient reduction of the fast form is
+    // gated the other way round, so exactly one of the two forms touches grad_weight.
+    auto run_family = [&](int fam, const View& cv0, const View& cv1, const int* gate) -> int {
+        auto plan_rows = [&](TileLaunch& L, const OpGeom geom) -> int {
+            int e = fill_plan(c, &L, s.M, s.CIg, s.COg, s.G, 1, geom);
+            if (e != kOk) return e;
+            TileParams& P = L.params;
+            P.a_row_coord = cv0.row_coord;
+            P.b_row_coord = wv.row_coord;
+            P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(wv);
+            P.pres = as_operand(xv);
+            P.out = x_addr(s);
+            P.out_f0 = gx;
+            P.p = p; P.q = p - 1.0f;
+            P.gate = gate;
+            if ((e = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return e;
+            if ((e = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return e;
+            return build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n);
+        };
+        int e;
+        if (fused) {
+            TileLaunch L;
+            if ((e = plan_rows(L, bwd_fused_geom(fam))) != kOk) return e;
+            L.params.side_out = side;
+            if ((e = launch_bwd_fused(fam, L, c.st)) != kOk) return e;
+            return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m),
+                                      accumulate_gw, gate ? gate : flag, gate != nullptr, c.st);
+        }
+        if (gx) {
+            TileLaunch L;
+            if ((e = plan_rows(L, bwd_x_geom(fam))) != kOk) return e;
+            if ((e = launch_bwd_x(fam, L, c.st)) != kOk) return e;
+        }
+        if (gw) {
+            // out (m = o, n = c), k = (b, hw)
+            TileLaunch L;
+            const OpGeom geom = bwd_w_geom(fam);
+            if ((e = fill_plan(c, &L, s.COg, s.CIg, static_cast<int>(s.M), s.G, 1, geom)) != kOk) return e;
+            TileParams& P = L.params;
+            P.a_row_coord = cv0.row_coord;
+            P.b_row_coord = xv.row_coord;
+            P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(xv);
+            P.pres = as_operand(wv);
+            P.out = w_addr(s);
+            P.out_f0 = gw;
+            P.p = p; P.q = p - 1.0f;
+            P.gate = gate;
+            if ((e = build_map(&L.map_a0, cv0, Layout::KMajor)) != kOk) return e;
+            if ((e = build_map(&L.map_a1, cv1, Layout::KMajor)) != kOk) return e;
+            if ((e = build_map(&L.map_b, xv, Layout::KMajor, geom.tile_n)) != kOk) return e;
+            if ((e = launch_bwd_w(fam, L, c.st)) != kOk) return e;
+        }
+        return kOk;
     };
-    if (fused) {
-        float* side = c.bump.take<float>(side_floats);
-        if (!side) return kWorkspace;
-        TileLaunch L;
-        if ((r = plan_rows(L, bwd_fused_geom(iq))) != kOk) return r;
-        L.params.side_out = side;
-        if ((r = launch_bwd_fused(iq, L, c.st)) != kOk) return r;
-        return launch_side_reduce(side, gw, static_cast<long long>(s.CO) * s.CIg, static_cast<int>(tiles_m),
-                                  accumulate_gw, c.st);
+    auto gen_views = [&](float* a, float* b, View* v0, View* v1) {
+        *v0 = View{a, gen_pitch, gen_rows, s.G, gen_pitch, gen_rows * gen_pitch, 1};
+        *v1 = View{b, gen_pitch, gen_rows, s.G, gen_pitch, gen_rows * gen_pitch, 1};
+    };
+
+    if (iq >= 0) {
+        float* c0 = c.bump.take<float>(int_floats);
+        if (!c0) return kWorkspace;
+        const View cv = View{c0, s.COg, s.M, s.G, int_pitch, s.M * int_pitch, 1};
+        if ((r = launch_coef_int(go, y, c0, s, static_cast<int>(int_pitch), iq, flag, flag_next, c.st)) != kOk) return r;
+        if ((r = run_family(iq, cv, cv, nullptr)) != kOk) return r;
+        if (!guarded) return kOk;
+        // second form, gated by the flag: 1 / y and g as coefficients, 2^(q lg2(|t| / y)) per pair
+        float* r0 = c.bump.take<float>(gen_floats);
+        float* r1 = c.bump.take<float>(gen_floats);
+        if (!r0 || !r1) return kWorkspace;
+        View v0, v1;
+        gen_views(r0, r1, &v0, &v1);
+        if ((r = launch_coef_gen(go, y, r0, r1, s, static_cast<int>(gen_pitch), gen_rows, p - 1.0f, false, flag, c.st)) != kOk)
+            return r;
+        return run_family(-2, v0, v1, flag);
     }
-    if (gx) {
-        TileLaunch L;
-        if ((r = plan_rows(L, bwd_x_geom(iq))) != kOk) return r;
-        if ((r = launch_bwd_x(iq, L, c.st)) != kOk) return r;
-    }
-    if (gw) {
-        // out (m = o, n = c), k = (b, hw)
-        TileLaunch L;
-        const OpGeom geom = bwd_w_geom(iq);
-        if ((r = fill_plan(c, &L, s.COg, s.CIg, static_cast<int>(s.M), s.G, 1, geom)) != kOk) return r;
-        TileParams& P = L.params;
-        P.a_row_coord = cv0.row_coord;
-        P.b_row_coord = xv.row_coord;
-        P.a0 = as_operand(cv0); P.a1 = as_operand(cv1); P.b = as_operand(xv);
-        P.pres = as_operand(wv);
-        P.out = w_addr(s);
-        P.out_f0 = gw;
-        P.p = p; P.q = p - 1.0f;
-        if ((r = build_map(&L.map_a0, cv0, Layout::KMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_a1, cv1, Layout::KMajor)) != kOk) return r;
-        if ((r = build_map(&L.map_b, xv, Layout::KMajor, geom.tile_n)) != kOk) return r;
-        if ((r = launch_bwd_w(iq, L, c.st)) != kOk) return r;
-    }
-    return kOk;
+    float* c0 = c.bump.take<float>(gen_floats);
+    float* c1 = c.bump.take<float>(gen_floats);
+    if (!c0 || !c1) return kWorkspace;
+    View v0, v1;
+    gen_views(c0, c1, &v0, &v1);
+    if ((r = launch_coef_gen(go, y, c0, c1, s, static_cast<int>(gen_pitch), gen_rows, p - 1.0f, iq == -1, nullptr, c.st)) != kOk)
+        return r;
+    return run_family(iq, v0, v1, nullptr);
 }
 
 int norm_dist_backward(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
@@ -739,7 +785,7 @@ LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float*
     char* base = nullptr;
     if ((r = noalloc_scratch_address(&base)) != kOk) return r;
     Arena fixed{base + kNoAllocStatusBytes, kNoAllocScratchBytes - kNoAllocStatusBytes,
-                reinterpret_cast<int*>(base), nullptr, nullptr, false, nullptr};
+                reinterpret_cast<int*>(base), nullptr, nullptr, 0u, false, nullptr};
     c.arena = &fixed;
     c.bump = Bump{fixed.base, 0, fixed.capacity};
     View xv, wv;

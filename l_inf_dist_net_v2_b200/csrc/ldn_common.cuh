@@ -73,6 +73,7 @@ struct TileParams {
     float q;                    // op specific (p - 1 for backward)
     const float* col_sub;       // optional per-output-channel epilogue of the no-grad p = inf kernels:
     const float* col_add;       //   stored value = (result - col_sub[channel]) + col_add[channel]; either may be null
+    const int* gate;            // not null: the kernel returns at once unless *gate != 0
     float* side_out;            // fused backward: per-row-tile column sums [tile_m][g][k][n] (else null)
     float* partials;            // stream-K scratch: [grid][2][arrays][kTileElems]
     int* status;                // device status word (0 = ok)
@@ -168,6 +169,7 @@ struct Arena {
     int* status_host;  // pinned host mirror used when checking
     void* call_mutex;  // std::mutex*: held for the length of one entry-point call, so that two host threads that
                        // use the same stream cannot interleave launches that share the scratch block
+    unsigned range_calls;  // calls that used the range guard of the integer-p backward (its two flag words alternate)
     bool graph_used;   // a call was issued on this arena while its stream was being captured
     void* retired;     // std::vector<void*>*: earlier blocks that captured graphs may still refer to
 };

@@ -5,6 +5,8 @@ namespace ldn {
 namespace {
 constexpr int kBlock = 256;
 constexpr int kRescanChunk = 1024;  // outputs a block of rescan_kernel handles in one pass (a multiple of kBlock / 8)
+// grid of a kernel that usually returns at once (gated): small, the grid-stride loops cover the rest when it runs
+inline unsigned gated_blocks(unsigned blocks, const int* gate) { return (gate && blocks > 592u) ? 592u : blocks; }
 inline unsigned blocks_for(long long n) {
     long long b = (n + kBlock - 1) / kBlock;
     if (b < 1) b = 1;
@@ -99,34 +101,51 @@ __device__ __forceinline__ long long y_offset(const Shape& s, const CanonIdx& q)
     return ((b * s.G + q.g) * s.COg + q.c) * s.HW + hw;
 }
 
+// Range guard of the integer-q coefficient g / y^q: *flag is raised when some y^-q is outside [kRqMin, kRqMax]
+// (beyond: y^-q overflows or |t|^q <= y^q goes denormal; below: the coefficient loses its bits); the first thread
+// also clears the word the next call will use.  flag may be null (q = 0).
+constexpr float kRqMin = 1e-30f, kRqMax = 1e24f;
+__device__ __forceinline__ bool rq_unsafe(float rq) { return !(rq >= kRqMin && rq <= kRqMax); }
+
 __global__ void coef_int_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ coef,
-                                Shape s, int pitch, int iq) {
+                                Shape s, int pitch, int iq, int* flag, int* flag_next) {
     const long long total = static_cast<long long>(s.G) * s.M * s.COg;
+    if (flag_next && blockIdx.x == 0 && threadIdx.x == 0) *flag_next = 0;
+    bool bad = false;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const CanonIdx q = canon_idx(i, s.COg, s.M);
         const long long src = y_offset(s, q);
         const float r = 1.0f / y[src];
-        float v = go[src];
-        for (int k = 0; k < iq; ++k) v *= r;
-        coef[(static_cast<long long>(q.g) * s.M + q.m) * pitch + q.c] = v;
+        float rq = 1.0f;
+        for (int k = 0; k < iq; ++k) rq *= r;
+        bad |= rq_unsafe(rq);
+        coef[(static_cast<long long>(q.g) * s.M + q.m) * pitch + q.c] = go[src] * rq;
     }
+    if (flag && bad) *flag = 1;
 }
 
 // flat fast paths (HW == 1, G == 1, pitch == COg: source and destination have the same element order)
 __global__ void coef_int_flat_kernel(const float4* __restrict__ go, const float4* __restrict__ y,
-                                     float4* __restrict__ coef, long long n4, int iq) {
+                                     float4* __restrict__ coef, long long n4, int iq, int* flag, int* flag_next) {
+    if (flag_next && blockIdx.x == 0 && threadIdx.x == 0) *flag_next = 0;
+    bool bad = false;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const float4 yv = y[i];
-        float4 v = go[i];
+        const float4 gv = go[i];
         const float4 r = make_float4(1.0f / yv.x, 1.0f / yv.y, 1.0f / yv.z, 1.0f / yv.w);
+        float4 rq = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
         for (int k = 0; k < iq; ++k) {
-            v.x *= r.x; v.y *= r.y; v.z *= r.z; v.w *= r.w;
+            rq.x *= r.x; rq.y *= r.y; rq.z *= r.z; rq.w *= r.w;
         }
-        coef[i] = v;
+        bad |= rq_unsafe(rq.x) | rq_unsafe(rq.y) | rq_unsafe(rq.z) | rq_unsafe(rq.w);
+        coef[i] = make_float4(gv.x * rq.x, gv.y * rq.y, gv.z * rq.z, gv.w * rq.w);
     }
+    if (flag && bad) *flag = 1;
 }
 __global__ void coef_gen_flat_kernel(const float4* __restrict__ go, const float4* __restrict__ y,
-                                     float4* __restrict__ rinv, float4* __restrict__ gcp, long long n4, float q, bool fold) {
+                                     float4* __restrict__ rinv, float4* __restrict__ gcp, long long n4, float q, bool fold,
+                                     const int* gate) {
+    if (gate && *gate == 0) return;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const float4 yv = y[i];
         rinv[i] = fold ? make_float4(-q * log2f(yv.x), -q * log2f(yv.y), -q * log2f(yv.z), -q * log2f(yv.w))
@@ -139,7 +158,9 @@ __global__ void coef_gen_flat_kernel(const float4* __restrict__ go, const float4
 // pitch, a multiple of 32): padding gets the offset -1e30 (folded form) or the factor 0 (1 / y form), which sends
 // the power to (almost) zero whatever |t| the zero-filled partner operand produces, and a zero gradient factor.
 __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ rinv,
-                                float* __restrict__ gcp, Shape s, int pitch, long long rows_pad, float q, bool fold) {
+                                float* __restrict__ gcp, Shape s, int pitch, long long rows_pad, float q, bool fold,
+                                const int* gate) {
+    if (gate && *gate == 0) return;
     const long long total = static_cast<long long>(s.G) * rows_pad * pitch;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const CanonIdx ci = canon_idx(i, pitch, rows_pad);
@@ -231,8 +252,10 @@ __global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const
         }
 }
 
+// gate (may be null): the kernel runs only if (*gate != 0) == run_if_nonzero
 __global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles,
-                                   bool accumulate) {
+                                   bool accumulate, const int* gate, bool run_if_nonzero) {
+    if (gate && (*gate != 0) != run_if_nonzero) return;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
         float s = 0.0f;
         for (int t = 0; t < tiles; ++t) s += part[t * count + i];
@@ -329,29 +352,31 @@ static bool flat_ok(const Shape& s, int pitch, const void* a, const void* b) {
            ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
 }
 
-int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, cudaStream_t st) {
+int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, int* flag,
+                    int* flag_next, cudaStream_t st) {
     if (flat_ok(s, pitch, go, y)) {
         const long long n4 = static_cast<long long>(s.M) * s.COg / 4;
         coef_int_flat_kernel<<<blocks_for(n4), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
                                                               reinterpret_cast<const float4*>(y),
-                                                              reinterpret_cast<float4*>(coef), n4, iq);
+                                                              reinterpret_cast<float4*>(coef), n4, iq, flag, flag_next);
         LDN_LAUNCH_RET();
     }
-    coef_int_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, coef, s, pitch, iq);
+    coef_int_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, coef, s, pitch, iq, flag,
+                                                                                flag_next);
     LDN_LAUNCH_RET();
 }
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
-                    long long rows_pad, float q, bool fold, cudaStream_t st) {
+                    long long rows_pad, float q, bool fold, const int* gate, cudaStream_t st) {
     if (flat_ok(s, pitch, go, y) && rows_pad == s.M) {
         const long long n4 = static_cast<long long>(s.M) * s.COg / 4;
-        coef_gen_flat_kernel<<<blocks_for(n4), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
+        coef_gen_flat_kernel<<<gated_blocks(blocks_for(n4), gate), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
                                                               reinterpret_cast<const float4*>(y),
                                                               reinterpret_cast<float4*>(rinv),
-                                                              reinterpret_cast<float4*>(gcp), n4, q, fold);
+                                                              reinterpret_cast<float4*>(gcp), n4, q, fold, gate);
         LDN_LAUNCH_RET();
     }
-    coef_gen_kernel<<<blocks_for((long long)s.G * rows_pad * pitch), kBlock, 0, st>>>(go, y, rinv, gcp, s, pitch,
-                                                                                   rows_pad, q, fold);
+    coef_gen_kernel<<<gated_blocks(blocks_for((long long)s.G * rows_pad * pitch), gate), kBlock, 0, st>>>(
+        go, y, rinv, gcp, s, pitch, rows_pad, q, fold, gate);
     LDN_LAUNCH_RET();
 }
 
@@ -368,8 +393,10 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
     LDN_LAUNCH_RET();
 }
 
-int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, cudaStream_t st) {
-    side_reduce_kernel<<<blocks_for(count), kBlock, 0, st>>>(part, gw, count, tiles, accumulate);
+int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, const int* gate,
+                       bool run_if_nonzero, cudaStream_t st) {
+    side_reduce_kernel<<<gated_blocks(blocks_for(count), run_if_nonzero ? gate : nullptr), kBlock, 0, st>>>(
+        part, gw, count, tiles, accumulate, gate, run_if_nonzero);
     LDN_LAUNCH_RET();
 }
 

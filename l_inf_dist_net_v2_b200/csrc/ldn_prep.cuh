@@ -17,14 +17,16 @@ int launch_canon_bounds(const float* xl, const float* xu, float* lc, float* uc, 
                         cudaStream_t st);
 // wc[g][o][pitch] <- w[(g COg + o) CIg + c]
 int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStream_t st);
-// integer p - 1 = iq:  coef[g][m][pitch] <- go / y^iq   (go, y in output layout)
-int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, cudaStream_t st);
+// integer p - 1 = iq:  coef[g][m][pitch] <- go / y^iq   (go, y in output layout).  flag (may be null): set to 1 when
+// some y^-iq is outside the range in which that coefficient times |t|^iq is accurate; flag_next (may be null): cleared.
+int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, int* flag,
+                    int* flag_next, cudaStream_t st);
 // general p: rinv[g][rows_pad][pitch] <- -q lg2 y (fold: the exponent offset of (|t| / y)^q) or 1 / y,
 // gcp[g][rows_pad][pitch] <- go; rows beyond M and columns beyond CO / G are padding (offset -1e30 resp. factor 0,
 // gradient factor 0)
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,
-                    long long rows_pad, float q, bool fold,
-                    cudaStream_t st);
+                    long long rows_pad, float q, bool fold, const int* gate,
+                    cudaStream_t st);  // gate (may be null): the kernel does nothing unless *gate != 0
 
 // Second step of the forward kernels that save an index: `pos` holds, per output, the id of the 32-channel
 // stage in which the extremum was first reached (or -1); replace it by the channel index | flag.
@@ -38,7 +40,9 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
                   cudaStream_t st, long long a_stride_k);
 
 // grad_weight of the fused backward: gw[i] = -sum_t part[t * count + i], t < tiles
-int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, cudaStream_t st);
+// gate (may be null): the kernel runs only if (*gate != 0) == run_if_nonzero
+int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, const int* gate,
+                       bool run_if_nonzero, cudaStream_t st);
 
 // p = inf backward: gx[b, idx] += v, gw[o, idx] -= v with v = pos >= 0 ? go : -go.  gx / gw may be null.
 int launch_inf_scatter(const float* go, const int* pos, float* gx, float* gw, const Shape& s, cudaStream_t st);

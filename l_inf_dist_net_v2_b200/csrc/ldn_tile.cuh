@@ -146,6 +146,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     int* ints = reinterpret_cast<int*>(smem + STAGES * STAGE + TileSmem<Op>::kSide);  // N_IN_SMEM ops
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE + TileSmem<Op>::kSide + TileSmem<Op>::kInts);
 
+    if (P.gate != nullptr && *P.gate == 0) return;
     const int tid = threadIdx.x;
     const int tn = thread_col<Op>(tid);
     const int tm = thread_row<Op>(tid);
@@ -476,6 +477,7 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
     constexpr int RN = Op::REG_N;
     constexpr int TN = 16 * RN;
     constexpr int TELEMS = kTileM * TN;
+    if (P.gate != nullptr && *P.gate == 0) return;
     const long long tile = blockIdx.x / kRegM;
     const int i = blockIdx.x % kRegM;
     const int KT = P.kt;

@@ -684,3 +684,36 @@ def test_eval_layer_in_one_kernel_matches_the_separate_steps(C, shape):
             assert torch.equal(fused_x_only, plain[0])
         lib.ldn_set_max_ctas(0)
     C.check_status()
+
+
+@pytest.mark.parametrize("p", [8.0, 9.0, 3.0])
+@pytest.mark.parametrize("scale", [1e-6, 1e-4, 1.0, 1e4, 3e5])
+def test_integer_p_backward_at_extreme_scales(C, p, scale):
+    """The integer-p backward multiplies g / y^(p-1) by |t|^(p-1); for outputs around 1e-5 or 1e5 that product leaves
+    the fp32 range although the gradient g (|t| / y)^(p-1) itself is of ordinary size (the reference keeps the
+    normalised form, norm_dist_cuda.cu:238-243).  The library detects such outputs and recomputes in the normalised
+    form: gradients must stay finite and accurate at every scale.  Targets: float64 evaluation of the definition."""
+    shape = (70, 96, 40, 2, 1)
+    x, w, g = make_inputs(shape, 9)
+    x, w = (x * scale).astype(np.float32), (w * scale).astype(np.float32)
+    B, CI, CO, G, HW = shape
+    xd = x.astype(np.float64).reshape(B, G, 1, CI // G)
+    wd = w.astype(np.float64).reshape(G, CO // G, CI // G)
+    t = xd - wd[None]                                         # B, G, COg, CIg
+    yd = (np.abs(t) ** p).sum(-1) ** (1.0 / p)                # B, G, COg
+    y32 = yd.reshape(B, CO, 1).astype(np.float32)
+    term = g.astype(np.float64).reshape(B, G, CO // G, 1) * np.sign(t) * (np.abs(t) / yd[..., None]) ** (p - 1)
+    gx_ref = term.sum(2).reshape(B, CI, 1)
+    gw_ref = -term.sum(0).reshape(CO, CI // G)
+    tol = 1e-5 if scale == 1.0 else 1e-4
+    gx, gw = run_backward(C, g, x, w, dev(y32), p, G)
+    for got, ref_ in ((gx, gx_ref), (gw, gw_ref)):
+        got = got.cpu().numpy()
+        assert np.isfinite(got).all(), (p, scale)
+        assert rel_to_max(got, ref_) < tol, (p, scale, rel_to_max(got, ref_))
+    _, gw_only = run_backward(C, g, x, w, dev(y32), p, G, want_gx=False)
+    assert rel_to_max(gw_only.cpu().numpy(), gw_ref) < tol, (p, scale)
+    gx_only = torch.full(x.shape, float("nan"), device="cuda")
+    C.norm_dist_backward_input(dev(g), dev(x), dev(w), dev(y32), gx_only, G, p)
+    assert rel_to_max(gx_only.cpu().numpy(), gx_ref) < tol, (p, scale)
+    C.check_status()
