@@ -182,7 +182,8 @@ __global__ void coef_gen_kernel(const float* __restrict__ go, const float* __res
 // blockIdx.x = (sample, group); blockIdx.y walks that pair's CO/G * HW outputs in chunks, so the index arithmetic
 // per output is one division by HW (none for fully connected layers) and, for those, a block keeps rereading one
 // input row, which stays in the L1 cache: only the weight pieces come from L2.
-__global__ void rescan_kernel(int mode, Operand a0, Operand a1, Operand b, const float* __restrict__ y,
+template <int mode>
+__global__ void rescan_kernel(Operand a0, Operand a1, Operand b, const float* __restrict__ y,
                               int* __restrict__ pos, Shape s, long long a_stride_k) {
     const int kpad = (s.CIg + 3) & ~3;
     const int q = threadIdx.x & 7;
@@ -388,8 +389,10 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
     if (cohw > 0x7fffffffLL || bg > 0x7fffffffLL) return kBadArgument;
     long long chunks = (cohw + kRescanChunk - 1) / kRescanChunk;
     if (chunks > 65535) chunks = 65535;  // the kernel strides over the rest
-    rescan_kernel<<<dim3(static_cast<unsigned>(bg), static_cast<unsigned>(chunks)), kBlock, 0, st>>>(mode, a0, a1, b, y,
-                                                                                                      pos, s, a_stride_k);
+    const dim3 grid(static_cast<unsigned>(bg), static_cast<unsigned>(chunks));
+    if (mode == 0) rescan_kernel<0><<<grid, kBlock, 0, st>>>(a0, a1, b, y, pos, s, a_stride_k);
+    else if (mode == 1) rescan_kernel<1><<<grid, kBlock, 0, st>>>(a0, a1, b, y, pos, s, a_stride_k);
+    else rescan_kernel<2><<<grid, kBlock, 0, st>>>(a0, a1, b, y, pos, s, a_stride_k);
     LDN_LAUNCH_RET();
 }
 
