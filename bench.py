@@ -63,6 +63,9 @@ def parse_args():
     ap.add_argument("--reserve-sms", type=int, default=8,
                     help="N > 1, model steps: SMs the persistent distance kernels leave free while gradient collectives "
                          "are in flight; the collectives run in an NCCL group limited to as many CTAs (0: no limit)")
+    ap.add_argument("--no-shard-updates", action="store_true",
+                    help="N > 1, model training: every rank updates whole parameters after an all-reduce (default: "
+                         "reduce-scatter, update of the rank's 1/N slice, all-gather)")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"],
                     help="model training workloads: Adam as the reference driver uses it, or plain SGD lr 0.02")
     ap.add_argument("--model-global-batch", type=int, default=4096)
@@ -593,7 +596,7 @@ class TrainStep:
     with targets, loss, backward, gradient exchange, optimiser step; the loss value goes back to the host."""
 
     def __init__(self, kind, p, batch, rank, world, device, optimizer="adam", reserve_sms=0, comm_group=None,
-                 eps=None):
+                 eps=None, shard_updates=False):
         import l_inf_dist_net_v2_b200 as ldn
         from l_inf_dist_net_v2_b200.parallel import OverlappedDataParallel
         self.net = build_model(kind, p, device)
@@ -604,7 +607,7 @@ class TrainStep:
         # first layer's exchange (exposed) on the default group at full width, the rest on the CTA-limited group
         self.ddp = OverlappedDataParallel(self.net, factory, group=comm_group,
                                           first_group=torch.distributed.group.WORLD if comm_group is not None else None,
-                                          reserve_sms=reserve_sms)
+                                          reserve_sms=reserve_sms, shard_updates=shard_updates)
         gen = torch.Generator().manual_seed(1000 + rank)
         self.xh = torch.rand(batch, *IMAGE, generator=gen).pin_memory()
         self.th = torch.randint(0, 10, (batch,), generator=gen).pin_memory()
@@ -700,7 +703,8 @@ def model_block(args, rank, world, local_rank, comm_group):
     if gb % world != 0:
         return {"error": f"global batch {gb} is not divisible by {world} ranks"}
     step = TrainStep("hybrid", math.inf, gb // world, rank, world, dev, optimizer="adam",
-                     reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group)
+                     reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group,
+                     shard_updates=not args.no_shard_updates)
     reps = 10 if world == 1 else 20
     launches0 = lib.ldn_kernel_launches()
     for _ in range(3):
@@ -713,9 +717,10 @@ def model_block(args, rank, world, local_rank, comm_group):
            "samples_per_s": round(gb * reps / (ms * 1e-3), 1), "optimizer": step.optimizer_name,
            "library_kernels_per_step": launches, "h2d_bytes_per_step": step.h2d, "d2h_bytes_per_step": step.d2h,
            "exchange": "none" if world == 1 else
-           f"NCCL all-reduce (mean) per parameter, started after backward in forward order, each layer's update deferred "
-           f"to just before its next forward; {args.reserve_sms} SMs left free by the distance kernels while "
-           f"collectives are in flight"}
+           ("NCCL reduce-scatter (mean) per parameter, update of the rank's 1/N slice, all-gather"
+            if not args.no_shard_updates else "NCCL all-reduce (mean) per parameter") +
+           f", started after backward in forward order, each layer's update deferred to just before its next forward; "
+           f"{args.reserve_sms} SMs left free by the distance kernels while collectives are in flight"}
     if world > 1:
         step.ddp.exchange = False  # same step without the collectives: what the exchange costs
         for _ in range(2):
@@ -761,7 +766,8 @@ def run_model(args, rank, world, local_rank, comm_group):
     if train:
         p = p_value(args.p)
         step = TrainStep(kind, p, B, rank, world, dev, optimizer=args.optimizer,
-                         reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group)
+                         reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group,
+                         shard_updates=not args.no_shard_updates)
         h2d, d2h = step.h2d, step.d2h
         per_step = B
     else:

@@ -89,7 +89,7 @@ class OverlappedDataParallel:
     At p = inf a layer's backward pass is a scatter of a few hundred microseconds while its weight gradient is
     60-100 MB, so there is no backward work to hide the all-reduce behind.  Instead:
 
-      * `step()` (after backward) starts one all-reduce (mean) per parameter in FORWARD order and marks every layer's
+      * `step()` (after backward) starts the exchange of every parameter in FORWARD order and marks every layer's
         update as due; nothing waits;
       * a layer's own optimiser applies its update in a forward pre-hook, just before that layer is used again, after
         waiting for that layer's collectives only.  So only the first layer's exchange is exposed; the later layers'
@@ -98,32 +98,54 @@ class OverlappedDataParallel:
       * the first layer's collectives use `first_group` (default: `group`); the others use `group`, which may be a
         CTA-limited NCCL group (nccl_group_with_cta_limit): while those are in flight the persistent distance kernels
         leave `reserve_sms` SMs free (ldn_set_max_ctas) for them -- a kernel that takes every SM would otherwise
-        either keep the collective waiting or lose SMs to it in mid-flight.
+        either keep the collective waiting or lose SMs to it in mid-flight;
+      * `shard_updates=True`: large parameters are exchanged as reduce-scatter + all-gather instead of one all-reduce
+        (the same bytes on the wire), and between the two every rank updates only its 1/world slice of the parameter,
+        with optimiser state for that slice only.  The update is an elementwise map, so the parameters are the same
+        as with the full update on every rank, but the memory-bound optimiser pass (28 bytes per parameter for Adam)
+        shrinks by the world size.  A layer's slice update and all-gather are issued one layer ahead on a side stream.
 
     `optimizer_factory(params)` builds one optimiser per layer (any torch.optim optimiser, or optim.FusedAdam /
-    FusedSGD).  Call `finish()` before evaluating, checkpointing or reading parameters: it applies what is still due
-    and, like DistributedDataParallel's buffer broadcast, copies rank 0's buffers (MeanShift running means) to all ranks.
+    FusedSGD); with shard_updates its parameters are 1-D slices that alias the layer's parameters.  Call `finish()`
+    before evaluating, checkpointing or reading parameters: it applies what is still due and, like
+    DistributedDataParallel's buffer broadcast, copies rank 0's buffers (MeanShift running means) to all ranks.
     """
 
-    SMALL = 4 << 20  # pending bytes below which the distance kernels take all SMs again
+    SMALL = 4 << 20  # pending bytes below which the distance kernels take all SMs again; smallest sharded parameter
 
-    def __init__(self, model, optimizer_factory, group=None, first_group=None, reserve_sms=0, set_max_ctas=None):
+    def __init__(self, model, optimizer_factory, group=None, first_group=None, reserve_sms=0, set_max_ctas=None,
+                 shard_updates=False):
         self.model = model
         self.group = group
         self.first_group = first_group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.reserve_sms = reserve_sms if self.world > 1 else 0
         self._set_max_ctas = set_max_ctas
         self._sm_count = None
         self._capped = False
         self.units = []
         self.exchange = self.world > 1
+        self.shard = bool(shard_updates) and self.world > 1
+        self._side = None
         for module in model.modules():
             params = [q for q in module.parameters(recurse=False) if q.requires_grad]
             if not params:
                 continue
-            unit = {"module": module, "params": params, "optimizer": optimizer_factory(params), "pending": [],
-                    "bytes": 0, "due": False}
+            unit = {"module": module, "params": params, "pending": [], "gathers": [], "bytes": 0, "due": False,
+                    "ready": None, "slices": {}}
+            opt_params = []
+            for q in params:
+                n = q.numel()
+                if (self.shard and q.is_contiguous() and n % self.world == 0
+                        and n * q.element_size() >= self.SMALL):
+                    per = n // self.world
+                    piece = q.data.view(-1)[self.rank * per:(self.rank + 1) * per]
+                    unit["slices"][id(q)] = piece
+                    opt_params.append(piece)
+                else:
+                    opt_params.append(q)
+            unit["optimizer"] = optimizer_factory(opt_params)
             self.units.append(unit)
             module.register_forward_pre_hook(lambda mod, args, u=unit: self._apply(u))
 
@@ -138,22 +160,64 @@ class OverlappedDataParallel:
         self._set_max_ctas(self._sm_count - self.reserve_sms if on else 0)
         self._capped = on
 
-    def _apply(self, unit):
-        if not unit["due"]:
-            return
+    def _reduce(self, tensor, group, out=None):
+        """Starts the mean over ranks of `tensor` (into `out`, this rank's slice of it, if given).  Backends without
+        an averaging reduction or a reduce-scatter (gloo) sum with an all-reduce; the division follows the wait."""
+        nccl = dist.get_backend(group) == "nccl"
+        if nccl and out is not None:
+            return dist.reduce_scatter_tensor(out, tensor, op=dist.ReduceOp.AVG, group=group, async_op=True), None
+        op = dist.ReduceOp.AVG if nccl else dist.ReduceOp.SUM
+        return dist.all_reduce(tensor, op=op, group=group, async_op=True), (None if nccl else tensor)
+
+    def _update(self, unit):
+        """On the current stream: wait for the unit's gradient exchange, update, and (sharded parameters) start and
+        wait for the all-gather of the updated slices."""
         for work, summed in unit["pending"]:
             work.wait()
-            if summed is not None:  # backends without an averaging reduction
-                summed.grad.div_(self.world)
+            if summed is not None:
+                summed.div_(self.world)
         unit["pending"].clear()
         unit["bytes"] = 0
+        stream = torch.cuda.current_stream() if torch.cuda.is_available() else None
+        for q in unit["params"]:
+            piece = unit["slices"].get(id(q))
+            if piece is not None and q.grad is not None:
+                per = piece.numel()
+                piece.grad = q.grad.view(-1)[self.rank * per:(self.rank + 1) * per]
         unit["optimizer"].step()
         for q in unit["params"]:
+            piece = unit["slices"].get(id(q))
+            if piece is not None and q.grad is not None:
+                if self.exchange:
+                    work = dist.all_gather_into_tensor(q.data.view(-1), piece, group=unit["group"], async_op=True)
+                    work.wait()
+                piece.grad = None
+            if q.grad is not None and stream is not None and q.grad.is_cuda:
+                q.grad.record_stream(stream)  # the update may have run on the side stream
             q.grad = None
         unit["due"] = False
+
+    def _apply(self, unit):
+        if unit["due"]:
+            self._update(unit)
+        elif unit["ready"] is not None:
+            torch.cuda.current_stream().wait_event(unit["ready"])  # updated one layer ahead on the side stream
+            unit["ready"] = None
+        else:
+            return
         # kernels launched from here on are ordered behind every collective whose wait is already in the stream
         if self._capped and sum(u["bytes"] for u in self.units) < self.SMALL:
             self._cap(False)
+        if self.shard and torch.cuda.is_available():
+            # the next layer's slice update and all-gather, beside this layer's forward
+            nxt = next((u for u in self.units if u["due"]), None)
+            if nxt is not None and nxt["slices"]:
+                if self._side is None:
+                    self._side = torch.cuda.Stream()
+                with torch.cuda.stream(self._side):
+                    self._update(nxt)
+                    nxt["ready"] = torch.cuda.Event()
+                    nxt["ready"].record(self._side)
 
     # -- training-loop interface ------------------------------------------------------------------------------------
     def step(self):
@@ -164,11 +228,15 @@ class OverlappedDataParallel:
             grads = [q for q in unit["params"] if q.grad is not None]
             if self.exchange and grads:
                 group = (self.first_group if first and self.first_group is not None else self.group)
-                avg = dist.get_backend(group) == "nccl"
-                op = dist.ReduceOp.AVG if avg else dist.ReduceOp.SUM
+                unit["group"] = group
                 for q in grads:
-                    work = dist.all_reduce(q.grad, op=op, group=group, async_op=True)
-                    unit["pending"].append((work, None if avg else q))
+                    piece = unit["slices"].get(id(q))
+                    flat = q.grad.view(-1) if piece is not None else q.grad
+                    out = None
+                    if piece is not None:
+                        per = piece.numel()
+                        out = flat[self.rank * per:(self.rank + 1) * per]
+                    unit["pending"].append(self._reduce(flat, group, out))
                     unit["bytes"] += q.grad.numel() * q.grad.element_size()
                 first = False
             unit["due"] = True
@@ -178,6 +246,8 @@ class OverlappedDataParallel:
     def finish(self):
         for unit in self.units:
             self._apply(unit)
+        if self._side is not None:
+            torch.cuda.current_stream().wait_stream(self._side)
         self._cap(False)
         if self.world > 1:
             bufs = [b for b in self.model.buffers()]

@@ -66,7 +66,7 @@ def test_shard_bounds_rejects_uneven_batches():
     assert shard_bounds(4096, 3, 8) == (1536, 2048)
 
 
-def _overlap_worker(rank, world, port, out_dir):
+def _overlap_worker(rank, world, port, out_dir, shard=False):
     """Three training steps of a small hybrid model: OverlappedDataParallel (updates applied layer by layer before
     the next forward) against the plain order (backward, all-reduce of every gradient, one optimiser step)."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -86,7 +86,11 @@ def _overlap_worker(rank, world, port, out_dir):
     ldn.set_p_norm(net_b, float("inf"))
     loss_fn = ldn.losses.crossentropy()
     make = lambda params: torch.optim.Adam(params, lr=0.03, betas=(0.9, 0.99), eps=1e-10)  # noqa: E731
-    ddp = OverlappedDataParallel(net_a, make)
+    if shard:
+        OverlappedDataParallel.SMALL = 0  # shard every parameter whose size divides by the world size
+    ddp = OverlappedDataParallel(net_a, make, shard_updates=shard)
+    if shard:
+        assert sum(len(u["slices"]) for u in ddp.units) >= 4
     opt_b = make(list(net_b.parameters()))
     gen = torch.Generator().manual_seed(100 + rank)
     ok = True
@@ -121,5 +125,14 @@ def _overlap_worker(rank, world, port, out_dir):
 def test_overlapped_data_parallel_matches_plain_order_world2(tmp_path):
     port = _free_port()
     mp.spawn(_overlap_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"rank{r}.txt").read() == "ok"
+
+
+def test_overlapped_data_parallel_with_sharded_updates_world2(tmp_path):
+    """Every rank updates only its slice of each parameter (with optimiser state for that slice) and the slices are
+    gathered: the parameters must come out as with the full update on every rank."""
+    port = _free_port()
+    mp.spawn(_overlap_worker, args=(2, port, str(tmp_path), True), nprocs=2, join=True)
     for r in range(2):
         assert open(tmp_path / f"rank{r}.txt").read() == "ok"
