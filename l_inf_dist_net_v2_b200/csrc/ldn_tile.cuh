@@ -549,13 +549,15 @@ int launch_tile(const TileLaunch& L, cudaStream_t stream) {
         if (e != cudaSuccess) return cuda_status(e);
         configured[dev] = true;
     }
-    timing_before(stream);
+    // (a gated launch usually returns at once: the optional timing brackets the ungated kernels only)
+    const bool timed = L.params.gate == nullptr;
+    if (timed) timing_before(stream);
     if (HALF && L.params.M <= kTileM / 2)
         tile_kernel<Op, (HALF ? kRegM / 2 : kRegM)><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b,
                                                                                       L.params);
     else
         tile_kernel<Op><<<L.grid, kThreads, SMEM, stream>>>(L.map_a0, L.map_a1, L.map_b, L.params);
-    timing_after(stream);
+    if (timed) timing_after(stream);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_status(e);
     count_launches(1);

@@ -73,6 +73,14 @@ def average_scalars(*values, device=None, group=None):
     return t.tolist()
 
 
+class _null_context:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
 def nccl_group_with_cta_limit(max_ctas):
     """A second NCCL process group over all ranks whose collectives use at most `max_ctas` CTAs, so that they can run
     on the SMs the distance kernels are told to leave free (OverlappedDataParallel(reserve_sms=...))."""
@@ -103,7 +111,9 @@ class OverlappedDataParallel:
         (the same bytes on the wire), and between the two every rank updates only its 1/world slice of the parameter,
         with optimiser state for that slice only.  The update is an elementwise map, so the parameters are the same
         as with the full update on every rank, but the memory-bound optimiser pass (28 bytes per parameter for Adam)
-        shrinks by the world size.  A layer's slice update and all-gather are issued one layer ahead on a side stream.
+        shrinks by the world size.  The whole chain (reduce-scatter, slice update, all-gather, layer after layer in
+        forward order) is issued on a side stream by `step()`; a layer's forward pre-hook only waits for that layer's
+        all-gather.  Worth it from about four ranks on (the slice updates run on the reserved SMs).
 
     `optimizer_factory(params)` builds one optimiser per layer (any torch.optim optimiser, or optim.FusedAdam /
     FusedSGD); with shard_updates its parameters are 1-D slices that alias the layer's parameters.  Call `finish()`
@@ -198,48 +208,56 @@ class OverlappedDataParallel:
         unit["due"] = False
 
     def _apply(self, unit):
-        if unit["due"]:
-            self._update(unit)
-        elif unit["ready"] is not None:
-            torch.cuda.current_stream().wait_event(unit["ready"])  # updated one layer ahead on the side stream
+        if unit["ready"] is not None:
+            torch.cuda.current_stream().wait_event(unit["ready"])  # exchanged and updated on the side stream
             unit["ready"] = None
+            unit["bytes"] = 0
+        elif unit["due"]:
+            self._update(unit)
         else:
             return
         # kernels launched from here on are ordered behind every collective whose wait is already in the stream
         if self._capped and sum(u["bytes"] for u in self.units) < self.SMALL:
             self._cap(False)
-        if self.shard and torch.cuda.is_available():
-            # the next layer's slice update and all-gather, beside this layer's forward
-            nxt = next((u for u in self.units if u["due"]), None)
-            if nxt is not None and nxt["slices"]:
-                if self._side is None:
-                    self._side = torch.cuda.Stream()
-                with torch.cuda.stream(self._side):
-                    self._update(nxt)
-                    nxt["ready"] = torch.cuda.Event()
-                    nxt["ready"].record(self._side)
 
     # -- training-loop interface ------------------------------------------------------------------------------------
     def step(self):
         """After backward: start the exchange (forward order) and make every layer's update due; the update itself
         happens before the layer's next forward, or in finish()."""
+        side = None
+        if self.shard and self.exchange and torch.cuda.is_available():
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            side = self._side
+            side.wait_stream(torch.cuda.current_stream())  # the gradients are complete
         first = True
         for unit in self.units:
             grads = [q for q in unit["params"] if q.grad is not None]
             if self.exchange and grads:
                 group = (self.first_group if first and self.first_group is not None else self.group)
                 unit["group"] = group
-                for q in grads:
-                    piece = unit["slices"].get(id(q))
-                    flat = q.grad.view(-1) if piece is not None else q.grad
-                    out = None
-                    if piece is not None:
-                        per = piece.numel()
-                        out = flat[self.rank * per:(self.rank + 1) * per]
-                    unit["pending"].append(self._reduce(flat, group, out))
-                    unit["bytes"] += q.grad.numel() * q.grad.element_size()
+                ctx = torch.cuda.stream(side) if side is not None else _null_context()
+                with ctx:
+                    for q in grads:
+                        piece = unit["slices"].get(id(q))
+                        flat = q.grad.view(-1) if piece is not None else q.grad
+                        out = None
+                        if piece is not None:
+                            per = piece.numel()
+                            out = flat[self.rank * per:(self.rank + 1) * per]
+                        unit["pending"].append(self._reduce(flat, group, out))
+                        unit["bytes"] += q.grad.numel() * q.grad.element_size()
+                    if side is not None:
+                        # the rest of this layer's chain right behind its reduce-scatter, so that the next layer's
+                        # collectives queue behind this layer's all-gather and not in front of it
+                        nbytes = unit["bytes"]
+                        self._update(unit)
+                        unit["bytes"] = nbytes
+                        unit["ready"] = torch.cuda.Event()
+                        unit["ready"].record(side)
                 first = False
-            unit["due"] = True
+            if unit["ready"] is None:
+                unit["due"] = True
         if self.exchange and sum(u["bytes"] for u in self.units[1:]) >= self.SMALL:
             self._cap(True)
 
