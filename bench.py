@@ -67,6 +67,10 @@ def parse_args():
                     help="N > 1, model training: reduce-scatter, update of the rank's 1/N slice, all-gather instead of "
                          "all-reduce and a full update on every rank (measured slower on 2 GPUs: the slice updates "
                          "share the reserved SMs with the collectives)")
+    ap.add_argument("--bwd-chunks", type=int, default=4,
+                    help="N > 1, layer step at finite p: ranges of output channels the backward pass is cut into, so that "
+                         "each range's grad_weight all-reduce overlaps the next range's kernels (1: one all-reduce after "
+                         "the backward pass)")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"],
                     help="model training workloads: Adam as the reference driver uses it, or plain SGD lr 0.02")
     ap.add_argument("--model-global-batch", type=int, default=4096)
@@ -241,11 +245,34 @@ def run_ours(args, rank, world, local_rank, comm_group=None):
         else:
             C.norm_dist_backward_input_weight(g, x, w, y, gx, gw, 1, pp)
 
+    # N > 1, finite p: the backward pass runs in ranges of output channels; the all-reduce of one range of grad_weight
+    # (on the CTA-limited NCCL group, the distance kernels leaving that many SMs free meanwhile) overlaps the next
+    # range's kernels, so only the last range's exchange is exposed.
+    chunks = args.bwd_chunks if (world > 1 and not math.isinf(p)) else 1
+    if CO % max(chunks, 1) != 0:
+        chunks = 1
+    sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
+    reserve = args.reserve_sms if (comm_group is not None and chunks > 1) else 0
+
     def step():
         fwd()
-        bwd()
-        if world > 1:
-            allreduce_mean_([gw])
+        if chunks <= 1:
+            bwd()
+            if world > 1:
+                allreduce_mean_([gw])
+            return
+        per = CO // chunks
+        works = []
+        for ci in range(chunks):
+            C.norm_dist_backward_channels(g, x, w, y, gx, gw, p, ci * per, per, ci > 0)
+            works.append(dist.all_reduce(gw[ci * per:(ci + 1) * per], op=dist.ReduceOp.AVG,
+                                         group=comm_group if ci + 1 < chunks else None, async_op=True))
+            if reserve and ci == 0:
+                lib.ldn_set_max_ctas(sm_total - reserve)
+        if reserve:
+            lib.ldn_set_max_ctas(0)
+        for wk in works:
+            wk.wait()
 
     # public-API step with host buffers
     w_param = w.clone().requires_grad_()
@@ -385,7 +412,10 @@ def run_ours(args, rank, world, local_rank, comm_group=None):
         "config": {"workload": f"norm_dist layer fwd+bwd {B}x{CI}->{CO} per rank, p={args.p}, G=1, HW=1",
                    "p": args.p, "batch_per_rank": B, "in_features": CI, "out_features": CO,
                    "pairs_per_step_per_rank": pairs, "passes_per_pair": 3,
-                   "exchange": "NCCL all-reduce(mean) of grad_weight" if world > 1 else "none",
+                   "exchange": ("none" if world == 1 else "NCCL all-reduce(mean) of grad_weight after the backward pass"
+                                if chunks <= 1 else
+                                f"NCCL all-reduce(mean) of grad_weight in {chunks} ranges of output channels, each started "
+                                f"behind its range's backward kernels ({reserve} SMs left free meanwhile)"),
                    "l2": "256 MiB buffer overwritten before every timed step"},
         "samples_per_s": round(world * B * args.steps / (total_ms * 1e-3), 1),
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "ms_per_step": round(total_e2e / args.steps, 4),

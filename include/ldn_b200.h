@@ -177,6 +177,19 @@ LDN_API int ldn_norm_dist_backward_input_weight(const float* grad_output, const 
                                         const float* output, int B, int CO, int CI, int G, int HW,
                                         float* grad_input, float* grad_weight, float p, ldn_stream_t stream);
 
+/*
+ * ldn_norm_dist_backward_input_weight for a range of output channels [co_begin, co_begin + co_count) of an ungrouped
+ * layer (no counterpart in the reference): grad_output and output are the whole layer's (B, CO, HW) arrays, weight and
+ * grad_weight the whole (CO, CI) arrays; rows co_begin.. of grad_weight are written, and grad_input receives the
+ * range's contribution -- overwritten, or added to what is there when accumulate_input != 0.  Calling it for
+ * consecutive ranges (the first with accumulate_input = 0) gives the full backward pass in pieces, so that a
+ * data-parallel caller can start the all-reduce of one piece of grad_weight while the next piece is computed.
+ */
+LDN_API int ldn_norm_dist_backward_channels(const float* grad_output, const float* input, const float* weight,
+                                            const float* output, int B, int CO, int CI, int HW, int co_begin,
+                                            int co_count, float* grad_input, float* grad_weight, float p,
+                                            int accumulate_input, ldn_stream_t stream);
+
 /* ---- p = inf -------------------------------------------------------------------------------- */
 
 /* Replaces inf_dist::forward_nograd (core/cuda/norm_dist.h:17-18): y = max(1e-10, max |t|). */

@@ -21,6 +21,7 @@ SIGNATURES = {
     "ldn_norm_dist_forward_with_max": [_c_float_p, _c_float_p, _c_float_p, _i, _i, _i, _i, _i, _c_float_p, _f, _s],
     "ldn_norm_dist_backward_input": [_c_float_p] * 4 + [_i] * 5 + [_c_float_p, _f, _s],
     "ldn_norm_dist_backward_input_weight": [_c_float_p] * 4 + [_i] * 5 + [_c_float_p, _c_float_p, _f, _s],
+    "ldn_norm_dist_backward_channels": [_c_float_p] * 4 + [_i] * 6 + [_c_float_p, _c_float_p, _f, _i, _s],
     "ldn_inf_dist_forward_nograd": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _s],
     "ldn_inf_dist_forward": [_c_float_p, _c_float_p] + [_i] * 5 + [_c_float_p, _c_int_p, _s],
     "ldn_inf_dist_backward_input": [_c_float_p, _c_int_p] + [_i] * 5 + [_c_float_p, _s],

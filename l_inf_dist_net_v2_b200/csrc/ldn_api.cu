@@ -71,6 +71,7 @@ int check_shape(int B, int CO, int CI, int G, int HW, Shape* s) {
     if (B == 0 || HW == 0) return kEmptyBatch;
     s->B = B; s->CO = CO; s->CI = CI; s->G = G; s->HW = HW;
     s->CIg = CI / G; s->COg = CO / G;
+    s->co_src = CO; s->co_off = 0;
     s->M = static_cast<long long>(B) * HW;
     if (s->M > 0x7fffffffLL) return kBadArgument;
     return kOk;
@@ -262,7 +263,7 @@ int int_power(float e) {
 // the normalised form 2^(q lg2(|t| / y)) by the general-p kernels, launched behind the fast ones with that flag as a
 // gate (they return at once when it is clear, which is always for networks' usual value ranges).
 int norm_dist_backward_part(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
-                            float* gw, float p, ldn_stream_t stream, bool accumulate_gw) {
+                            float* gw, float p, ldn_stream_t stream, bool accumulate_gw, bool accumulate_gx = false) {
     const DeviceCtx* ctx;
     int r = get_device_ctx(&ctx);
     if (r != kOk) return r;
@@ -319,6 +320,12 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
             P.out_f0 = gx;
             P.p = p; P.q = p - 1.0f;
             P.gate = gate;
+            P.accumulate_out = accumulate_gx ? 1 : 0;
+            if (accumulate_gx && guarded && gate == nullptr) {
+                // adding to grad_input: exactly one of the two forms may run (the fast one only while the flag is clear)
+                P.gate = flag;
+                P.gate_invert = 1;
+            }
             if ((e = build_map(&L.map_a0, cv0, Layout::RowMajor)) != kOk) return e;
             if ((e = build_map(&L.map_a1, cv1, Layout::RowMajor)) != kOk) return e;
             return build_map(&L.map_b, wv, Layout::KMajor, geom.tile_n);
@@ -391,7 +398,7 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
 }
 
 int norm_dist_backward(const float* go, const float* x, const float* w, const float* y, const Shape& s, float* gx,
-                       float* gw, float p, ldn_stream_t stream) {
+                       float* gw, float p, ldn_stream_t stream, bool accumulate_gx = false) {
     if (!go || !x || !w || !y || (!gx && !gw)) return kBadArgument;
     if (!(p > 0.0f) || isinf(p) || isnan(p)) return kBadArgument;
     // The fused kernel keeps one copy of grad_weight per 128-row tile as scratch.  A batch whose copies would
@@ -407,14 +414,15 @@ int norm_dist_backward(const float* go, const float* x, const float* w, const fl
                 Shape sc = s;
                 sc.B = static_cast<int>(s.B - b0 < chunk_b ? s.B - b0 : chunk_b);
                 sc.M = static_cast<long long>(sc.B) * s.HW;
-                const size_t oy = static_cast<size_t>(b0) * s.CO * s.HW, ox = static_cast<size_t>(b0) * s.CI * s.HW;
-                const int r = norm_dist_backward_part(go + oy, x + ox, w, y + oy, sc, gx + ox, gw, p, stream, b0 > 0);
+                const size_t oy = static_cast<size_t>(b0) * s.co_src * s.HW, ox = static_cast<size_t>(b0) * s.CI * s.HW;
+                const int r = norm_dist_backward_part(go + oy, x + ox, w, y + oy, sc, gx + ox, gw, p, stream, b0 > 0,
+                                                      accumulate_gx);
                 if (r != kOk) return r;
             }
             return kOk;
         }
     }
-    return norm_dist_backward_part(go, x, w, y, s, gx, gw, p, stream, false);
+    return norm_dist_backward_part(go, x, w, y, s, gx, gw, p, stream, false, accumulate_gx);
 }
 
 int inf_forward(const float* x, const float* w, const Shape& s, float* y, int* pos, ldn_stream_t stream,
@@ -612,6 +620,24 @@ LDN_API int ldn_norm_dist_backward_input_weight(const float* grad_output, const 
     if (r != kOk) return r;
     if (!grad_weight) return kBadArgument;
     return norm_dist_backward(grad_output, input, weight, output, s, grad_input, grad_weight, p, stream);
+}
+
+LDN_API int ldn_norm_dist_backward_channels(const float* grad_output, const float* input, const float* weight,
+                                            const float* output, int B, int CO, int CI, int HW, int co_begin,
+                                            int co_count, float* grad_input, float* grad_weight, float p,
+                                            int accumulate_input, ldn_stream_t stream) {
+    Shape s;
+    if (co_begin < 0 || co_count <= 0 || co_begin > CO - co_count) return kBadArgument;
+    int r = check_shape(B, co_count, CI, 1, HW, &s);
+    if (r == kEmptyBatch) return empty_result(grad_weight ? grad_weight + static_cast<size_t>(co_begin) * CI : nullptr,
+                                              co_count, CI, 1, stream);
+    if (r != kOk) return r;
+    if (!grad_input || !grad_weight || CO <= 0) return kBadArgument;
+    s.co_src = CO;
+    s.co_off = co_begin;
+    const size_t woff = static_cast<size_t>(co_begin) * CI;
+    return norm_dist_backward(grad_output, input, weight + woff, output, s, grad_input, grad_weight + woff, p, stream,
+                              accumulate_input != 0);
 }
 
 LDN_API int ldn_inf_dist_forward_nograd(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,

@@ -73,7 +73,9 @@ struct TileParams {
     float q;                    // op specific (p - 1 for backward)
     const float* col_sub;       // optional per-output-channel epilogue of the no-grad p = inf kernels:
     const float* col_add;       //   stored value = (result - col_sub[channel]) + col_add[channel]; either may be null
-    const int* gate;            // not null: the kernel returns at once unless *gate != 0
+    const int* gate;            // not null: the kernel returns at once unless (*gate != 0) == (gate_invert == 0)
+    int gate_invert;
+    int accumulate_out;         // backward kernels: add to the output instead of overwriting it
     float* side_out;            // fused backward: per-row-tile column sums [tile_m][g][k][n] (else null)
     float* partials;            // stream-K scratch: [grid][2][arrays][kTileElems]
     int* status;                // device status word (0 = ok)

@@ -597,7 +597,9 @@ struct BwdLayout {
     }
     __device__ static float diff(float pres, float b) { return WEIGHT ? b - pres : pres - b; }
     __device__ static void store(float v, int m, int n, int g, const TileParams& P) {
-        P.out_f0[out_offset(P.out, m, n, g)] = WEIGHT ? -v : v;
+        float* dst = P.out_f0 + out_offset(P.out, m, n, g);
+        v = WEIGHT ? -v : v;
+        *dst = P.accumulate_out ? *dst + v : v;
     }
 };
 

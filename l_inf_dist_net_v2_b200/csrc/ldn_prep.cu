@@ -98,6 +98,7 @@ __global__ void canon_w_kernel(const float* __restrict__ w, float* __restrict__ 
 // thread index runs over (g, m, o) with o fastest; source offset in output layout
 __device__ __forceinline__ long long y_offset(const Shape& s, const CanonIdx& q) {
     const long long b = q.m / s.HW, hw = q.m % s.HW;
+    if (s.co_src != s.CO) return (b * s.co_src + s.co_off + q.c) * s.HW + hw;  // channel range, G == 1
     return ((b * s.G + q.g) * s.COg + q.c) * s.HW + hw;
 }
 
@@ -349,7 +350,7 @@ int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStr
     LDN_LAUNCH_RET();
 }
 static bool flat_ok(const Shape& s, int pitch, const void* a, const void* b) {
-    return s.HW == 1 && s.G == 1 && pitch == s.COg && (s.COg & 3) == 0 &&
+    return s.HW == 1 && s.G == 1 && s.co_src == s.CO && pitch == s.COg && (s.COg & 3) == 0 &&
            ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
 }
 

@@ -8,6 +8,9 @@ struct Shape {
     int B, CO, CI, G, HW;
     int CIg, COg;
     long long M;  // B * HW
+    // A range of output channels of a wider layer (G == 1 only): grad_output / output rows are co_src channels long and
+    // this problem's channel o is their channel co_off + o.  co_src == CO, co_off == 0: the whole layer.
+    int co_src, co_off;
 };
 
 // xc[g][m][pitch] <- x[((b G + g) CIg + c) HW + hw],  m = b HW + hw

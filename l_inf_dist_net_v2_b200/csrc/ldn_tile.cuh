@@ -146,7 +146,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
     int* ints = reinterpret_cast<int*>(smem + STAGES * STAGE + TileSmem<Op>::kSide);  // N_IN_SMEM ops
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE + TileSmem<Op>::kSide + TileSmem<Op>::kInts);
 
-    if (P.gate != nullptr && *P.gate == 0) return;
+    if (P.gate != nullptr && (*P.gate != 0) == (P.gate_invert != 0)) return;
     const int tid = threadIdx.x;
     const int tn = thread_col<Op>(tid);
     const int tm = thread_row<Op>(tid);
@@ -268,6 +268,11 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                 }
         }
 
+        // A wait that runs out: the thread records the status and returns; the host reads the status word
+        // (ldn_check_status).  All threads of a CTA wait on the same barrier with the same budget, so they give up
+        // together.  (Variants that made the verdict CTA-uniform -- through the barrier that follows, or a shared flag
+        // checked behind it -- or that first waited for the loads still in flight cost the forward and general-p
+        // kernels 1 - 7 % in same-GPU A/B runs and were dropped: the schedule of this loop is that sensitive.)
         if (!mbar_wait_bounded(&full[ls % STAGES], (ls / STAGES) & 1)) {
             atomicExch(P.status, static_cast<int>(kDeviceTimeout));
             return;
@@ -477,7 +482,7 @@ tile_fixup_kernel(const TileParams P, const int main_grid) {
     constexpr int RN = Op::REG_N;
     constexpr int TN = 16 * RN;
     constexpr int TELEMS = kTileM * TN;
-    if (P.gate != nullptr && *P.gate == 0) return;
+    if (P.gate != nullptr && (*P.gate != 0) == (P.gate_invert != 0)) return;
     const long long tile = blockIdx.x / kRegM;
     const int i = blockIdx.x % kRegM;
     const int KT = P.kt;

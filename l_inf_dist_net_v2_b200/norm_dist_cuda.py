@@ -161,6 +161,19 @@ def mean_shift_rows(x, running_mean, momentum, out):
         check(lib.ldn_mean_shift_rows(a, B, C, rm, float(momentum), y, None, _stream()), "mean_shift_rows")
 
 
+def norm_dist_backward_channels(grad_output, input, weight, output, grad_input, grad_weight, p, co_begin, co_count,
+                                accumulate_input):
+    """Not part of the reference's extension module: the finite-p backward pass of an ungrouped layer restricted to the
+    output channels [co_begin, co_begin + co_count); see ldn_norm_dist_backward_channels."""
+    g, a, w, y = _f(grad_output, "grad_output"), _f(input, "input"), _f(weight, "weight"), _f(output, "output")
+    gx, gw = _f(grad_input, "grad_input"), _f(grad_weight, "grad_weight")
+    B, CO, CI, HW = grad_output.size(0), output.size(1), input.size(1), input.size(2)
+    with torch.cuda.device(input.device):
+        check(lib.ldn_norm_dist_backward_channels(g, a, w, y, B, CO, CI, HW, co_begin, co_count, gx, gw, p,
+                                                  int(bool(accumulate_input)), _stream()),
+              "norm_dist_backward_channels")
+
+
 def inf_dist_forward_nograd_shifted(input, weight, output, sub, add, G):
     """Not part of the reference's extension module: inf_dist_forward_nograd with (y - sub[o]) + add[o] applied in the
     store; sub / add are (CO,) tensors or None."""

@@ -142,3 +142,4 @@ def test_two_host_threads_on_one_stream(lib):
     for _, _, yd, ref in cases:
         assert np.array_equal(yd.cpu().numpy(), ref)
     assert lib.ldn_check_status(stream) == 0
+

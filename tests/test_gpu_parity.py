@@ -717,3 +717,34 @@ def test_integer_p_backward_at_extreme_scales(C, p, scale):
     C.norm_dist_backward_input(dev(g), dev(x), dev(w), dev(y32), gx_only, G, p)
     assert rel_to_max(gx_only.cpu().numpy(), gx_ref) < tol, (p, scale)
     C.check_status()
+
+
+@pytest.mark.parametrize("shape", [(130, 200, 150, 1, 1), (64, 784, 1024, 1, 1), (9, 40, 96, 1, 5)])
+@pytest.mark.parametrize("p", [8.0, 37.5, 2.0])
+def test_backward_in_channel_ranges_matches_whole(C, shape, p):
+    """The finite-p backward in ranges of output channels (grad_input accumulated over the ranges, grad_weight written
+    range by range) against the whole-layer call and the checker; also at a scale where the integer form's range
+    guard switches to the normalised form, which must not be added twice."""
+    B, CI, CO, G, HW = shape
+    for scale in (1.0, 1e-5):
+        x, w, g = make_inputs(shape, 17)
+        x, w = (x * scale).astype(np.float32), (w * scale).astype(np.float32)
+        if scale == 1.0:
+            y = run_forward(C, x, w, p, G)
+        else:
+            t = x.astype(np.float64).transpose(0, 2, 1)[:, :, None, :] - w.astype(np.float64)[None, None]
+            y = dev(((np.abs(t) ** p).sum(-1) ** (1.0 / p)).transpose(0, 2, 1).astype(np.float32))
+        whole = run_backward(C, g, x, w, y, p, G)
+        gx = torch.full(x.shape, float("nan"), device="cuda")
+        gw = torch.full(w.shape, float("nan"), device="cuda")
+        bounds = [0, CO // 3, CO // 3 + 1, CO]
+        for i in range(3):
+            C.norm_dist_backward_channels(dev(g), dev(x), dev(w), y, gx, gw, p, bounds[i], bounds[i + 1] - bounds[i], i > 0)
+        tol = 1e-4 if scale != 1.0 else 2e-6
+        assert rel_to_max(gx.cpu().numpy(), whole[0].cpu().numpy()) < tol, (shape, p, scale)
+        assert rel_to_max(gw.cpu().numpy(), whole[1].cpu().numpy()) < tol, (shape, p, scale)
+        if scale == 1.0:
+            ogx, ogw = oracle.norm_dist_backward(g, x, w, y.cpu().numpy(), p, G)
+            assert rel_to_max(gx.cpu().numpy(), ogx) < rtol_for(p, True)
+            assert rel_to_max(gw.cpu().numpy(), ogw) < rtol_for(p, True)
+    C.check_status()
