@@ -67,10 +67,10 @@ def parse_args():
                     help="N > 1, model training: reduce-scatter, update of the rank's 1/N slice, all-gather instead of "
                          "all-reduce and a full update on every rank (measured slower on 2 GPUs: the slice updates "
                          "share the reserved SMs with the collectives)")
-    ap.add_argument("--bwd-chunks", type=int, default=4,
+    ap.add_argument("--bwd-chunks", type=int, default=1,
                     help="N > 1, layer step at finite p: ranges of output channels the backward pass is cut into, so that "
-                         "each range's grad_weight all-reduce overlaps the next range's kernels (1: one all-reduce after "
-                         "the backward pass)")
+                         "each range's grad_weight all-reduce overlaps the next range's kernels (default 1: one all-reduce "
+                         "after the backward pass; on 2 GPUs 2 / 4 / 8 ranges took 3.40 / 3.59 / 3.93 ms against 3.29)")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"],
                     help="model training workloads: Adam as the reference driver uses it, or plain SGD lr 0.02")
     ap.add_argument("--model-global-batch", type=int, default=4096)
