@@ -71,6 +71,8 @@ def parse_args():
                     help="N > 1, layer step at finite p: ranges of output channels the backward pass is cut into, so that "
                          "each range's grad_weight all-reduce overlaps the next range's kernels (default 1: one all-reduce "
                          "after the backward pass; on 2 GPUs 2 / 4 / 8 ranges took 3.40 / 3.59 / 3.93 ms against 3.29)")
+    ap.add_argument("--graph", action="store_true",
+                    help="one GPU, model training workloads: record the whole step in a CUDA graph and replay it")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "sgd"],
                     help="model training workloads: Adam as the reference driver uses it, or plain SGD lr 0.02")
     ap.add_argument("--model-global-batch", type=int, default=4096)
@@ -628,7 +630,7 @@ class TrainStep:
     with targets, loss, backward, gradient exchange, optimiser step; the loss value goes back to the host."""
 
     def __init__(self, kind, p, batch, rank, world, device, optimizer="adam", reserve_sms=0, comm_group=None,
-                 eps=None, shard_updates=False):
+                 eps=None, shard_updates=False, graph=False):
         import l_inf_dist_net_v2_b200 as ldn
         from l_inf_dist_net_v2_b200.parallel import OverlappedDataParallel
         self.net = build_model(kind, p, device)
@@ -636,10 +638,22 @@ class TrainStep:
         self.loss_fn = ldn.losses.hinge(mix=0.25) if kind == "mlp" else ldn.losses.crossentropy(mix=0)
         self.eps = eps if eps is not None else (8.0 / 255.0 if kind == "mlp" else 0.0345)
         factory, self.optimizer_name = make_optimizer_factory(optimizer)
+        self.graph = None
+        self.graph_launches = 0
+        self.use_graph = bool(graph) and world == 1
+        if self.use_graph:
+            # one GPU: the whole step (copies, forward, loss, backward, Adam with its step count on the device) is
+            # recorded once and replayed; nothing is deferred
+            from l_inf_dist_net_v2_b200.optim import FusedAdam
+            self.opt = FusedAdam(list(self.net.parameters()), lr=0.03, betas=(0.9, 0.99), eps=1e-10, capturable=True)
+            self.optimizer_name = "Adam lr 0.03 betas (0.9, 0.99) eps 1e-10 (one-kernel update, step count on the device)"
+            self.ddp = None
         # first layer's exchange (exposed) on the default group at full width, the rest on the CTA-limited group
-        self.ddp = OverlappedDataParallel(self.net, factory, group=comm_group,
-                                          first_group=torch.distributed.group.WORLD if comm_group is not None else None,
-                                          reserve_sms=reserve_sms, shard_updates=shard_updates)
+        if not self.use_graph:
+            self.ddp = OverlappedDataParallel(
+                self.net, factory, group=comm_group,
+                first_group=torch.distributed.group.WORLD if comm_group is not None else None,
+                reserve_sms=reserve_sms, shard_updates=shard_updates)
         gen = torch.Generator().manual_seed(1000 + rank)
         self.xh = torch.rand(batch, *IMAGE, generator=gen).pin_memory()
         self.th = torch.randint(0, 10, (batch,), generator=gen).pin_memory()
@@ -649,17 +663,46 @@ class TrainStep:
         self.h2d = self.xh.numel() * 4 + self.th.numel() * 8
         self.d2h = 4
 
-    def __call__(self):
+    def _eager(self):
         self.x.copy_(self.xh, non_blocking=True)
         self.t.copy_(self.th, non_blocking=True)
         logits, worst = self.net(self.x, targets=self.t, eps=self.eps)
         loss = self.loss_fn(logits, worst, self.t)
         loss.backward()
-        self.ddp.step()
+        if self.ddp is not None:
+            self.ddp.step()
+        else:
+            self.opt.step()
+            self.opt.zero_grad(set_to_none=True)
         self.loss_h.copy_(loss.detach().view(1), non_blocking=True)
 
+    def capture(self):
+        """Warm-up on the capture stream (scratch arenas and optimiser state reach their final size), then record."""
+        from l_inf_dist_net_v2_b200._lib import lib
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                self._eager()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        before = lib.ldn_kernel_launches()
+        with torch.cuda.graph(self.graph, stream=s):
+            self._eager()
+        self.graph_launches = int(lib.ldn_kernel_launches() - before)
+
+    def __call__(self):
+        if self.use_graph:
+            if self.graph is None:
+                self.capture()
+            self.graph.replay()
+        else:
+            self._eager()
+
     def finish(self):
-        self.ddp.finish()
+        if self.ddp is not None:
+            self.ddp.finish()
 
 
 class CertifySweep:
@@ -708,10 +751,12 @@ def _timed(fn, reps, world, dev):
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     e0.record()
     for _ in range(reps):
         fn()
     e1.record()
+    _timed.host_ms = (time.perf_counter() - t0) * 1e3  # host time to enqueue the work (this rank)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -742,11 +787,13 @@ def model_block(args, rank, world, local_rank, comm_group):
     for _ in range(3):
         step()
     ms = _timed(step, reps, world, dev)
+    host_ms = _timed.host_ms
     launches = int(lib.ldn_kernel_launches() - launches0) // (reps + 3)
     row = {"model": "HybridModel(depth=7, width=5120, hidden=512, identity_val=10.0), p=inf, cross-entropy on "
                     "worst-case logits, eps_train 0.0345",
            "global_batch": gb, "batch_per_rank": gb // world, "steps": reps, "ms_per_step": round(ms / reps, 3),
            "samples_per_s": round(gb * reps / (ms * 1e-3), 1), "optimizer": step.optimizer_name,
+           "host_enqueue_ms_per_step": round(host_ms / reps, 3),
            "library_kernels_per_step": launches, "h2d_bytes_per_step": step.h2d, "d2h_bytes_per_step": step.d2h,
            "exchange": "none" if world == 1 else
            ("NCCL reduce-scatter (mean) per parameter, update of the rank's 1/N slice, all-gather"
@@ -799,7 +846,7 @@ def run_model(args, rank, world, local_rank, comm_group):
         p = p_value(args.p)
         step = TrainStep(kind, p, B, rank, world, dev, optimizer=args.optimizer,
                          reserve_sms=args.reserve_sms if world > 1 else 0, comm_group=comm_group,
-                         shard_updates=args.shard_updates)
+                         shard_updates=args.shard_updates, graph=args.graph)
         h2d, d2h = step.h2d, step.d2h
         per_step = B
     else:
@@ -816,7 +863,10 @@ def run_model(args, rank, world, local_rank, comm_group):
     sampler.mark()
     launches0 = lib.ldn_kernel_launches()
     ms = _timed(step, args.steps, world, dev)
+    host_ms = _timed.host_ms
     launches = int(lib.ldn_kernel_launches() - launches0)
+    if train and step.use_graph:
+        launches = step.graph_launches * args.steps  # replays launch what the capture recorded
     clocks = sampler.stop()
     if train:
         step.finish()
@@ -837,8 +887,10 @@ def run_model(args, rank, world, local_rank, comm_group):
                                     % (model, B)),
                        "batch_per_rank": B, "l2": "working set 560 MB of weights per step, larger than L2"},
             "e2e": {"value": round(value, 1), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "api": "l_inf_dist_net_v2_b200 models + autograd + parallel.OverlappedDataParallel + optim"},
-            "gpu_launches": launches, "clocks": clocks}
+                    "api": "l_inf_dist_net_v2_b200 models + autograd + parallel.OverlappedDataParallel + optim" +
+                           (", whole step replayed from a CUDA graph" if (train and step.use_graph) else "")},
+            "gpu_launches": launches, "clocks": clocks,
+            "host_enqueue_ms_per_step": round(host_ms / args.steps, 3)}
 
 
 # ------------------------------------------------------------------------------------------------

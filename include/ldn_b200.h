@@ -137,6 +137,12 @@ LDN_API int ldn_probe_pipe(int kind, int iters, float* sink, unsigned long long*
 LDN_API int ldn_adam_update(int count, float* const* params, const float* const* grads, float* const* exp_avg,
                             float* const* exp_avg_sq, const long long* sizes, float lr, float beta1, float beta2,
                             float eps, int step, float grad_scale, ldn_stream_t stream);
+/* ldn_adam_update with the step count t (>= 1, as a float) read from device memory at kernel time, so that the launch
+ * can be recorded in a CUDA graph and replayed while the caller advances *step_device on the stream. */
+LDN_API int ldn_adam_update_device_step(int count, float* const* params, const float* const* grads,
+                                        float* const* exp_avg, float* const* exp_avg_sq, const long long* sizes, float lr,
+                                        float beta1, float beta2, float eps, const float* step_device, float grad_scale,
+                                        ldn_stream_t stream);
 LDN_API int ldn_sgd_update(int count, float* const* params, const float* const* grads, float* const* momentum_buf,
                            const long long* sizes, float lr, float momentum, float dampening, float weight_decay,
                            int nesterov, int first_step, float grad_scale, ldn_stream_t stream);

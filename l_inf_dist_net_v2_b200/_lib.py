@@ -38,6 +38,8 @@ SIGNATURES = {
     "ldn_mean_shift_rows": [_c_float_p, _i, _i, _c_float_p, _f, _c_float_p, _c_float_p, _s],
     "ldn_adam_update": [_i, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                         _f, _f, _f, _f, _i, _f, _s],
+    "ldn_adam_update_device_step": [_i, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                    ctypes.c_void_p, _f, _f, _f, _f, ctypes.c_void_p, _f, _s],
     "ldn_sgd_update": [_i, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                        _f, _f, _f, _f, _i, _i, _f, _s],
     "ldn_check_status": [_s],

@@ -31,6 +31,9 @@ struct AdamArgs {
     float step_size;           // lr / (1 - beta1^t)
     float inv_sqrt_bias2;      // 1 / sqrt(1 - beta2^t)
     float grad_scale;
+    float lr;
+    const float* step_dev;     // not null: t is read from device memory (a launch recorded in a CUDA graph must not
+                               // carry the step count as an argument), and the two factors above are derived from it
 };
 
 struct SgdArgs {
@@ -57,8 +60,14 @@ __device__ __forceinline__ void sgd_one(float& p, float g, float* m, const SgdAr
 }
 
 template <bool ADAM>
-__global__ void __launch_bounds__(256) update_kernel(const __grid_constant__ TensorList L, const AdamArgs aa,
+__global__ void __launch_bounds__(256) update_kernel(const __grid_constant__ TensorList L, const AdamArgs aa_in,
                                                      const SgdArgs sa) {
+    AdamArgs aa = aa_in;
+    if (ADAM && aa.step_dev != nullptr) {
+        const float t = *aa.step_dev;
+        aa.step_size = aa.lr / (1.0f - powf(aa.beta1, t));
+        aa.inv_sqrt_bias2 = rsqrtf(1.0f - powf(aa.beta2, t));
+    }
     const long long total_chunks = L.first_chunk[L.count];
     for (long long c = blockIdx.x; c < total_chunks; c += gridDim.x) {
         int t = 0;
@@ -167,6 +176,24 @@ using namespace ldn;
 
 extern "C" {
 
+LDN_API int ldn_adam_update_device_step(int count, float* const* params, const float* const* grads,
+                                        float* const* exp_avg, float* const* exp_avg_sq, const long long* sizes, float lr,
+                                        float beta1, float beta2, float eps, const float* step_device, float grad_scale,
+                                        ldn_stream_t stream) {
+    if (!step_device || !(beta1 >= 0.0f && beta1 < 1.0f) || !(beta2 >= 0.0f && beta2 < 1.0f)) return kBadArgument;
+    AdamArgs aa;
+    aa.beta1 = beta1;
+    aa.beta2 = beta2;
+    aa.eps = eps;
+    aa.step_size = 0.0f;
+    aa.inv_sqrt_bias2 = 0.0f;
+    aa.grad_scale = grad_scale;
+    aa.lr = lr;
+    aa.step_dev = step_device;
+    return run_update<true>(count, params, grads, exp_avg, exp_avg_sq, sizes, aa, SgdArgs{},
+                            reinterpret_cast<cudaStream_t>(stream));
+}
+
 LDN_API int ldn_adam_update(int count, float* const* params, const float* const* grads, float* const* exp_avg,
                             float* const* exp_avg_sq, const long long* sizes, float lr, float beta1, float beta2,
                             float eps, int step, float grad_scale, ldn_stream_t stream) {
@@ -178,6 +205,8 @@ LDN_API int ldn_adam_update(int count, float* const* params, const float* const*
     aa.step_size = static_cast<float>(lr / (1.0 - pow(static_cast<double>(beta1), step)));
     aa.inv_sqrt_bias2 = static_cast<float>(1.0 / sqrt(1.0 - pow(static_cast<double>(beta2), step)));
     aa.grad_scale = grad_scale;
+    aa.lr = lr;
+    aa.step_dev = nullptr;
     return run_update<true>(count, params, grads, exp_avg, exp_avg_sq, sizes, aa, SgdArgs{},
                             reinterpret_cast<cudaStream_t>(stream));
 }

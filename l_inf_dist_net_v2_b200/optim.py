@@ -42,14 +42,44 @@ class _Fused(torch.optim.Optimizer):
 
 
 class FusedAdam(_Fused):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, grad_scale=1.0):
+    """capturable=True keeps the step count in a float tensor on the device (as torch.optim.Adam(capturable=True)
+    does), advanced by a tensor operation and read by the update kernel, so that `step()` can be recorded in a CUDA
+    graph; run at least one step before capturing (it creates the state)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, grad_scale=1.0, capturable=False):
         if lr < 0 or eps < 0 or not (0 <= betas[0] < 1) or not (0 <= betas[1] < 1):
             raise ValueError("invalid Adam hyper-parameters")
-        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, grad_scale=grad_scale))
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, grad_scale=grad_scale, capturable=capturable))
+
+    def _step_capturable(self, group, params):
+        by_dev = {}
+        for q, g in self._select(group, params):
+            st = self.state[q]
+            if not st:
+                st["step"] = torch.zeros((), dtype=torch.float32, device=q.device)
+                st["exp_avg"] = torch.zeros_like(q, memory_format=torch.preserve_format)
+                st["exp_avg_sq"] = torch.zeros_like(q, memory_format=torch.preserve_format)
+            by_dev.setdefault(q.device, []).append((q, g, st))
+        for device, items in by_dev.items():
+            # one counter per launch: the tensors updated together share the first one's step tensor
+            steps = [st["step"] for _, _, st in items]
+            torch._foreach_add_(steps, 1.0)
+            ps = [q for q, _, _ in items]
+            with torch.cuda.device(device):
+                check(lib.ldn_adam_update_device_step(
+                    len(items), _ptr_array(ps), _ptr_array([g for _, g, _ in items]),
+                    _ptr_array([st["exp_avg"] for _, _, st in items]),
+                    _ptr_array([st["exp_avg_sq"] for _, _, st in items]),
+                    (ctypes.c_longlong * len(items))(*[q.numel() for q in ps]),
+                    group["lr"], group["betas"][0], group["betas"][1], group["eps"], steps[0].data_ptr(),
+                    group["grad_scale"], torch.cuda.current_stream().cuda_stream), "adam update")
 
     @torch.no_grad()
     def step(self, params=None):
         for group in self.param_groups:
+            if group.get("capturable"):
+                self._step_capturable(group, params)
+                continue
             by_step = {}
             for q, g in self._select(group, params):
                 st = self.state[q]

@@ -42,3 +42,57 @@ def test_certification_matches_reference_models(kind):
 
 def test_pgd_matches_reference_attack():
     mp.check_pgd(torch.device("cuda"))
+
+
+@pytest.mark.parametrize("p,adam_eps", [(8.0, 1e-10), (math.inf, 1e-3)])
+def test_whole_training_step_in_a_cuda_graph(p, adam_eps):
+    """Forward, loss, backward and the Adam update (step count on the device) of a small hybrid model recorded in one
+    CUDA graph: three warm-up steps plus four replays must leave the parameters where seven eager steps leave them.
+    (At p = inf the scatter backward adds with atomics, so gradients differ in their last bits from run to run; Adam
+    with the reference's eps = 1e-10 turns such noise on near-zero gradients into full-size steps, hence the larger
+    eps there: the comparison is about the graph, not about Adam's conditioning.)"""
+    import copy
+    import l_inf_dist_net_v2_b200 as ldn
+    from l_inf_dist_net_v2_b200.optim import FusedAdam
+    torch.manual_seed(0)
+    net_a = ldn.HybridModel(depth=4, width=64, input_dim=[1, 8, 8], hidden=32, identity_val=None).cuda()
+    net_b = copy.deepcopy(net_a)
+    loss_fn = ldn.losses.crossentropy()
+    gen = torch.Generator().manual_seed(5)
+    x = torch.rand(48, 1, 8, 8, generator=gen).cuda()
+    t = torch.randint(0, 10, (48,), generator=gen).cuda()
+
+    def make_step(net):
+        ldn.set_p_norm(net, p)
+        net.train()
+        opt = FusedAdam(list(net.parameters()), lr=0.01, betas=(0.9, 0.99), eps=adam_eps, capturable=True)
+
+        def step():
+            logits, worst = net(x, targets=t, eps=0.03)
+            loss_fn(logits, worst, t).backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+        return step
+
+    eager = make_step(net_b)
+    for _ in range(7):
+        eager()
+    step = make_step(net_a)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s):
+        step()
+    for _ in range(4):
+        graph.replay()
+    torch.cuda.synchronize()
+    for (name, qa), qb in zip(net_a.named_parameters(), net_b.parameters()):
+        # (p = inf: the scatter backward adds with atomics, so sums differ in the last bits between runs)
+        assert torch.allclose(qa, qb, rtol=1e-4, atol=1e-5), name
+    for ba, bb in zip(net_a.buffers(), net_b.buffers()):
+        assert torch.allclose(ba, bb, rtol=1e-5, atol=1e-6)

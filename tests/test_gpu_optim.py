@@ -63,3 +63,42 @@ def test_fused_update_of_a_subset_leaves_the_rest_alone():
     opt.step(params=[a[1], a[3]])
     for i, (q, q0) in enumerate(zip(a, before)):
         assert torch.equal(q, q0) != (i in (1, 3)), i
+
+
+def test_capturable_adam_in_a_cuda_graph_matches_torch():
+    """FusedAdam(capturable=True) keeps the step count on the device: its step can be recorded in a CUDA graph and
+    replayed; four replays must match four eager torch.optim.Adam steps on the same gradients."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from l_inf_dist_net_v2_b200.optim import FusedAdam
+    a, b = _params(3), _params(3)
+    fused = FusedAdam(a, lr=0.03, betas=(0.9, 0.99), eps=1e-10, capturable=True)
+    ref = torch.optim.Adam(b, lr=0.03, betas=(0.9, 0.99), eps=1e-10)
+    grads = [torch.zeros_like(q) for q in a]
+    for q, g in zip(a, grads):
+        q.grad = g
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+
+    def load(step):
+        gen = torch.Generator().manual_seed(50 + step)
+        for g, q in zip(grads, b):
+            g.copy_(torch.randn(*g.shape, generator=gen))
+            q.grad = g.clone()
+
+    load(0)
+    with torch.cuda.stream(s):
+        fused.step()           # creates the state; not part of the graph
+    torch.cuda.current_stream().wait_stream(s)
+    ref.step()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s):
+        fused.step()
+    for step in range(1, 5):
+        load(step)
+        graph.replay()
+        ref.step()
+        torch.cuda.synchronize()
+        for qa, qb in zip(a, b):
+            assert torch.allclose(qa, qb, rtol=3e-6, atol=3e-7), (step, tuple(qa.shape))
+    assert float(fused.state[a[0]]["step"]) == 5.0
