@@ -270,7 +270,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 
         // A wait that runs out: the thread records the status and returns; the host reads the status word
         // (ldn_check_status).  All threads of a CTA wait on the same barrier with the same budget, so they give up
-        // together.  (Variants that made the verdict CTA-uniform -- through the barrier that follows, or a shared flag
+        // together.  (Variants that made the outcome CTA-uniform -- through the barrier that follows, or a shared flag
         // checked behind it -- or that first waited for the loads still in flight cost the forward and general-p
         // kernels 1 - 7 % in same-GPU A/B runs and were dropped: the schedule of this loop is that sensitive.)
         if (!mbar_wait_bounded(&full[ls % STAGES], (ls / STAGES) & 1)) {
