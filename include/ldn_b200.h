@@ -74,6 +74,13 @@ LDN_API int ldn_reserve_scratch(ldn_stream_t stream, unsigned long long bytes);
 LDN_API void ldn_set_max_ctas(int max_ctas);
 
 /*
+ * Test hook: ldn_bound_inf_dist_forward computes both bounds and both indices in one pass when the reduction has at
+ * most 65534 stages of 32 channels (two 16-bit stage ids per output), else in one pass per bound.  This lowers that
+ * limit (0: always two passes; a negative value restores the default), so that tests reach the two-pass kernels.
+ */
+LDN_API void ldn_set_bound_one_pass_limit(int stages);
+
+/*
  * Scratch limit of the fused finite-p backward (bytes; 0 restores the default of 1 GiB).  The kernel keeps one
  * copy of grad_weight per 128 rows of the batch; a batch that would need more than the limit is processed in
  * chunks of whole samples whose weight gradients are added up.  No counterpart in the reference.

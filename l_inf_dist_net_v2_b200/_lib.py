@@ -49,7 +49,7 @@ SIGNATURES = {
     "ldn_probe_pipe": [_i, _i, _c_float_p, ctypes.c_void_p, _s],
 }
 OTHER_SYMBOLS = ["ldn_status_string", "ldn_version", "ldn_set_max_ctas", "ldn_kernel_launches", "ldn_set_trace_buffer",
-                 "ldn_enable_kernel_timing", "ldn_last_tile_kernel_ms", "ldn_set_fused_scratch_limit"]
+                 "ldn_enable_kernel_timing", "ldn_last_tile_kernel_ms", "ldn_set_fused_scratch_limit", "ldn_set_bound_one_pass_limit"]
 
 
 class LdnError(RuntimeError):
@@ -72,6 +72,8 @@ def load(path=LIB_PATH):
     lib.ldn_version.restype = ctypes.c_char_p
     lib.ldn_set_max_ctas.argtypes = [ctypes.c_int]
     lib.ldn_set_max_ctas.restype = None
+    lib.ldn_set_bound_one_pass_limit.argtypes = [ctypes.c_int]
+    lib.ldn_set_bound_one_pass_limit.restype = None
     lib.ldn_set_fused_scratch_limit.argtypes = [ctypes.c_ulonglong]
     lib.ldn_set_fused_scratch_limit.restype = None
     lib.ldn_enable_kernel_timing.argtypes = [ctypes.c_int]

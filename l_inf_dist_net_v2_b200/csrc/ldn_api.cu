@@ -15,6 +15,7 @@ int release_arenas();
 namespace {
 
 int g_max_ctas = 0;
+int g_bound_one_pass_stages = kBoundBothMaxStages;  // longest reduction (in 32-channel stages) the one-pass kernel takes
 // scratch the fused backward may use for its per-row-tile column sums (bytes); larger batches run in row chunks
 size_t g_side_limit = size_t(1) << 30;
 
@@ -475,7 +476,7 @@ int bound_forward(const float* xl, const float* xu, const float* w, const Shape&
     View wv;
     if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
     if (!pl) return run_forward(c, FwdKind::Bound, 0, lv, &uv, wv, s, yl, yu, nullptr, nullptr, nullptr, INFINITY);
-    if ((s.CIg + kTileK - 1) / kTileK <= kBoundBothMaxStages) {
+    if ((s.CIg + kTileK - 1) / kTileK <= g_bound_one_pass_stages) {
         // one pass: both bounds and the stage of each extremum, then the two index searches
         r = run_forward(c, FwdKind::BoundPosBoth, 0, lv, &uv, wv, s, yl, yu, pl, pu, nullptr, INFINITY);
         if (r != kOk) return r;
@@ -517,6 +518,10 @@ LDN_API const char* ldn_status_string(int status) {
 LDN_API const char* ldn_version(void) { return "ldn_b200 0.1 sm_100a"; }
 
 LDN_API void ldn_set_max_ctas(int max_ctas) { g_max_ctas = max_ctas > 0 ? max_ctas : 0; }
+
+LDN_API void ldn_set_bound_one_pass_limit(int stages) {
+    g_bound_one_pass_stages = (stages >= 0 && stages < kBoundBothMaxStages) ? stages : kBoundBothMaxStages;
+}
 
 LDN_API void ldn_set_fused_scratch_limit(unsigned long long bytes) {
     g_side_limit = bytes > 0 ? static_cast<size_t>(bytes) : size_t(1) << 30;

@@ -310,11 +310,14 @@ def test_inf_family_against_checker(C, shape):
         yL, yU = torch.empty_like(y), torch.empty_like(y)
         C.bound_inf_dist_forward_nograd(dev(xL), dev(xU), dev(w), yL, yU, G)
         assert np.array_equal(yL.cpu().numpy(), oyL) and np.array_equal(yU.cpu().numpy(), oyU), (shape, max_ctas)
-        pL, pU = torch.empty_like(pos), torch.empty_like(pos)
-        yL2, yU2 = torch.empty_like(y), torch.empty_like(y)
-        C.bound_inf_dist_forward(dev(xL), dev(xU), dev(w), yL2, yU2, pL, pU, G)
-        assert torch.equal(yL, yL2) and torch.equal(yU, yU2)
-        assert np.array_equal(pL.cpu().numpy(), opL) and np.array_equal(pU.cpu().numpy(), opU), (shape, max_ctas)
+        for one_pass_limit in (-1, 0):  # one pass for both bounds (default); one pass per bound (very long reductions)
+            lib.ldn_set_bound_one_pass_limit(one_pass_limit)
+            pL, pU = torch.empty_like(pos), torch.empty_like(pos)
+            yL2, yU2 = torch.empty_like(y), torch.empty_like(y)
+            C.bound_inf_dist_forward(dev(xL), dev(xU), dev(w), yL2, yU2, pL, pU, G)
+            assert torch.equal(yL, yL2) and torch.equal(yU, yU2)
+            assert np.array_equal(pL.cpu().numpy(), opL) and np.array_equal(pU.cpu().numpy(), opU), (shape, max_ctas)
+        lib.ldn_set_bound_one_pass_limit(-1)
     lib.ldn_set_max_ctas(0)
     # scatters
     gx = torch.full(x.shape, float("nan"), device="cuda")
