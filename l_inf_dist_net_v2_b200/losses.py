@@ -16,7 +16,7 @@ class hinge:
 
     def __call__(self, outputs, worst_outputs, targets):
         pos = worst_outputs.clamp(min=0)
-        return (1 - self.mix) * pos.amax(dim=1).mean() + self.mix * pos.mean()
+        return (1 - self.mix) * pos.max(dim=1)[0].mean() + self.mix * pos.mean()
 
 
 class crossentropy:
@@ -46,4 +46,4 @@ class mixture:
 
     def __call__(self, outputs, worst_outputs, targets):
         pos = worst_outputs.clamp(min=0, max=self.clip)
-        return pos.amax(dim=1).mean() + self.lam * F.cross_entropy(outputs, targets)
+        return pos.max(dim=1)[0].mean() + self.lam * F.cross_entropy(outputs, targets)

@@ -143,7 +143,7 @@ class OverlappedDataParallel:
             params = [q for q in module.parameters(recurse=False) if q.requires_grad]
             if not params:
                 continue
-            unit = {"module": module, "params": params, "pending": [], "gathers": [], "bytes": 0, "due": False,
+            unit = {"module": module, "params": params, "pending": [], "bytes": 0, "due": False,
                     "ready": None, "slices": {}}
             opt_params = []
             for q in params:
