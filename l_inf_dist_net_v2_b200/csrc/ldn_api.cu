@@ -94,6 +94,10 @@ struct Call {
     int cap;  // persistent CTAs
     const float* col_sub = nullptr;  // epilogue of the no-grad p = inf kernels (see TileParams)
     const float* col_add = nullptr;
+    const float* norm_rows = nullptr;  // separable normaliser of FwdPowNorm and its guard word (see TileParams)
+    const float* norm_cols = nullptr;
+    int* guard = nullptr;
+    const int* gate = nullptr;         // forward kernels launched while set return at once unless *gate != 0
     std::unique_lock<std::mutex> lock;  // the arena's call mutex, released when the entry point returns
 };
 
@@ -229,6 +233,12 @@ int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, c
         P.col_sub = c.col_sub;
         P.col_add = c.col_add;
     }
+    if (kind == FwdKind::PowNorm && pres == nullptr) {
+        P.norm_rows = c.norm_rows;
+        P.norm_cols = c.norm_cols;
+        P.guard = c.guard;
+    }
+    P.gate = c.gate;
     const Layout la = inplace ? Layout::KMajor : Layout::RowMajor;
     if ((r = build_map(&L.map_a0, a0, la)) != kOk) return r;
     if ((r = build_map(&L.map_a1, a1 ? *a1 : a0, la)) != kOk) return r;
@@ -246,6 +256,9 @@ int run_forward(Call& c, FwdKind kind, int ip, const View& a0, const View* a1, c
 // The folded general-p backward evaluates 2^(q lg2|t| - q lg2 y): the absolute error of the logarithm (~2e-7) is
 // multiplied by q, so beyond this q the kernels take the logarithm of |t| / y (near 1 for the terms that matter).
 constexpr float kFoldMaxQ = 64.0f;
+
+// Largest p for which the forward pass normalises by the separable bound of the maximum (ldn_norm_dist_forward).
+constexpr float kBoundNormMaxP = 100.0f;
 
 // integer template value the reference dispatch would use for exponent e (norm_dist.cpp:17-35)
 int int_power(float e) {
@@ -566,9 +579,17 @@ LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B
     const int ip = normalised ? -1 : int_power(p);
     const FwdKind kind = normalised ? FwdKind::PowNorm : (ip >= 1 ? FwdKind::PowInt : FwdKind::PowGen);
     const bool inplace = x_inplace_kmajor(input, s) && fwd_variant_supported(kind, ip);
+    // Up to this p the normaliser is the separable bound max|x| + max|w| of max|t| (two row reductions instead of a
+    // full max pass); beyond, a bound a few per cent above the true maximum already underflows the sum, so the exact
+    // maximum is computed first, as the reference does.
+    const bool bound_norm = normalised && p <= kBoundNormMaxP;
+    const long long xrows = inplace ? s.HW : s.M;
+    const long long xgroups = inplace ? static_cast<long long>(s.B) * s.G : s.G;
+    const size_t norm_floats = static_cast<size_t>(xrows * xgroups) + static_cast<size_t>(s.CO);
     const size_t ybytes = pad256(sizeof(float) * static_cast<size_t>(B) * CO * HW);
     size_t need = (inplace ? 0 : x_scratch_bytes(input, s)) + w_scratch_bytes(weight, s) +
-                  2 * partial_bytes(cap_for(ctx), 1) + (normalised ? ybytes : 0);
+                  (bound_norm ? 3 : 2) * partial_bytes(cap_for(ctx), 1) + (normalised ? ybytes : 0) +
+                  (bound_norm ? 2 * pad256(norm_floats * sizeof(float)) : 0);
     Call c;
     if ((r = begin_call(&c, stream, need)) != kOk) return r;
     View xv, wv;
@@ -580,6 +601,27 @@ LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B
                            inplace);
     float* mbuf = c.bump.take<float>(static_cast<size_t>(B) * CO * HW);
     if (!mbuf) return kWorkspace;
+    if (bound_norm) {
+        float* xa = c.bump.take<float>(static_cast<size_t>(xrows * xgroups));
+        float* wa = c.bump.take<float>(static_cast<size_t>(s.CO));
+        if (!xa || !wa) return kWorkspace;
+        // the guard word: two words of the arena's status block used in turn, each call clears the next call's
+        const unsigned turn = c.arena->norm_calls++ & 1u;
+        int* flag = c.arena->status + 3 + turn;
+        int* flag_next = c.arena->status + 3 + (turn ^ 1u);
+        const Operand xop = inplace ? Operand{input, 1, static_cast<long long>(s.CIg) * s.HW} : as_operand(xv);
+        if ((r = launch_row_absmax(xop, xrows, s.CIg, static_cast<int>(xgroups), inplace ? s.HW : 1, xa, flag_next,
+                                   c.st)) != kOk)
+            return r;
+        if ((r = launch_row_absmax(as_operand(wv), s.COg, s.CIg, s.G, 1, wa, nullptr, c.st)) != kOk) return r;
+        c.norm_rows = xa;
+        c.norm_cols = wa;
+        c.guard = flag;
+        r = run_forward(c, FwdKind::PowNorm, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, nullptr, p, inplace);
+        if (r != kOk) return r;
+        // the exact form behind it, gated by the guard word: runs only when some sum came out too small
+        c.gate = flag;
+    }
     r = run_forward(c, FwdKind::Inf, 0, xv, nullptr, wv, s, mbuf, nullptr, nullptr, nullptr, nullptr, INFINITY, inplace);
     if (r != kOk) return r;
     return run_forward(c, FwdKind::PowNorm, -1, xv, nullptr, wv, s, output, nullptr, nullptr, nullptr, mbuf, p, inplace);
@@ -816,7 +858,7 @@ LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float*
     char* base = nullptr;
     if ((r = noalloc_scratch_address(&base)) != kOk) return r;
     Arena fixed{base + kNoAllocStatusBytes, kNoAllocScratchBytes - kNoAllocStatusBytes,
-                reinterpret_cast<int*>(base), nullptr, nullptr, 0u, false, nullptr};
+                reinterpret_cast<int*>(base), nullptr, nullptr, 0u, 0u, false, nullptr};
     c.arena = &fixed;
     c.bump = Bump{fixed.base, 0, fixed.capacity};
     View xv, wv;

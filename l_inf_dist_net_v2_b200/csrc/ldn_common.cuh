@@ -71,6 +71,9 @@ struct TileParams {
     int* out_i1;
     float p;                    // the exponent the op was called with
     float q;                    // op specific (p - 1 for backward)
+    const float* norm_rows;     // FwdPowNorm with a separable normaliser M[m, n] = max(norm_rows[g][m] + norm_cols[g'][n], 1e-10)
+    const float* norm_cols;     //   (row-wise largest magnitudes of the two operands: an upper bound of max |t|); else null
+    int* guard;                 // raised by that form when a sum comes out too small for the normaliser to have been adequate
     const float* col_sub;       // optional per-output-channel epilogue of the no-grad p = inf kernels:
     const float* col_add;       //   stored value = (result - col_sub[channel]) + col_add[channel]; either may be null
     const int* gate;            // not null: the kernel returns at once unless (*gate != 0) == (gate_invert == 0)
@@ -171,6 +174,7 @@ struct Arena {
     int* status_host;  // pinned host mirror used when checking
     void* call_mutex;  // std::mutex*: held for the length of one entry-point call, so that two host threads that
                        // use the same stream cannot interleave launches that share the scratch block
+    unsigned norm_calls;   // calls that used the guarded normaliser of the p > 10 forward (its two flag words alternate)
     unsigned range_calls;  // calls that used the range guard of the integer-p backward (its two flag words alternate)
     bool graph_used;   // a call was issued on this arena while its stream was being captured
     void* retired;     // std::vector<void*>*: earlier blocks that captured graphs may still refer to

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kProbeThreads, 4) mix_probe_kernel(int iters, 
                 col[i] = __ffma2_rn(sv, make_float2(g, g), col[i]);
             } else {
                 const float2 l = make_float2(lg2_approx(fabsf(x[i].x - w0)), lg2_approx(fabsf(x[i].y - w0)));
-                acc[i] = __fadd2_rn(acc[i], ex2_mixed2<3, kMufuEveryFwd>(
+                acc[i] = __fadd2_rn(acc[i], ex2_mixed2<4, kMufuEveryFwd>(
                                                  __ffma2_rn(make_float2(q, q), l, make_float2(off, off)), i));
             }
         }

@@ -91,9 +91,11 @@ __device__ __forceinline__ float2 ex2_mixed2(float2 e, int sel) {
     if ((sel % EVERY) == 0) return make_float2(ex2_approx(e.x), ex2_approx(e.y));
     return ex2_fma2<DEG>(e);
 }
-// measured best on B200: the forward (deg-3 polynomial) sends one exponential in 8 to MUFU, the backward
-// (deg-4 polynomial, two accumulations per term) every second one
-constexpr int kMufuEveryFwd = 8;
+// measured best on B200 (degree-4 polynomial in both): the forward sends one exponential in 3 to MUFU (3.23 ms
+// for the sum pass of 512 x 3072 -> 5120 against 3.27 / 3.31 / 3.43 with one in 4 / 6 / 8), the backward, with two
+// accumulations per term, every second one.  (A degree-3 polynomial in the forward was 9 % faster but left the
+// output 2e-6 off, which the backward multiplies by p - 1: the gradients then missed 1e-4 on small problems.)
+constexpr int kMufuEveryFwd = 3;
 constexpr int kMufuEveryBwd = 2;
 
 // |t|^IP by repeated multiplication, IP in 1..8
@@ -279,8 +281,19 @@ struct FwdPowGen : FwdLayout {
     }
 };
 
-// sum of (|t| / M)^p with a per-output normaliser M read from P.pres (layout of the output);
-// resident value = -p lg2 M.   y = M (sum + (1e-10 / M)^p)^(1/p)
+// sum of (|t| / M)^p with a per-output normaliser M; resident value = -p lg2 M;  y = M (sum + (1e-10 / M)^p)^(1/p).
+// The value of y does not depend on M (it cancels), only the fp32 range of the terms does.  M is either read from
+// P.pres (layout of the output: the exact maximum of |t|, or the caller's array), or -- P.norm_rows set -- the
+// separable upper bound max_c |x| + max_c |w| of that maximum, which costs two small row reductions instead of a
+// full max pass; a sum below kNormGuard then means the bound was too loose for this output's terms to stay well
+// inside the fp32 range, and the kernel raises P.guard (the caller recomputes with the exact maximum).
+constexpr float kNormGuard = 1e-27f;
+__device__ __forceinline__ float pow_norm_of(const TileParams& P, int m, int n, int g, long long off) {
+    if (P.norm_rows == nullptr) return P.pres.ptr[off];
+    const int gb = P.b_group_mod > 0 ? g % P.b_group_mod : g;
+    return fmaxf(P.norm_rows[static_cast<long long>(g) * P.M + m] + P.norm_cols[static_cast<long long>(gb) * P.N + n], kEps);
+}
+
 struct FwdPowNorm : FwdLayout {
     static constexpr bool SHORT_STAGES = true;
     static constexpr int NUM_A = 1, NF = 1, NI = 0;
@@ -297,7 +310,7 @@ struct FwdPowNorm : FwdLayout {
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
             const float2 l = make_float2(lg2_approx(fabsf(a[k] - b0[k])), lg2_approx(fabsf(a[k] - b1[k])));
-            acc = __fadd2_rn(acc, ex2_mixed2<3, kMufuEveryFwd>(__ffma2_rn(pp, l, cm), sel + k));
+            acc = __fadd2_rn(acc, ex2_mixed2<4, kMufuEveryFwd>(__ffma2_rn(pp, l, cm), sel + k));
         }
         s0 = acc.x;
         s1 = acc.y;
@@ -306,15 +319,16 @@ struct FwdPowNorm : FwdLayout {
     __device__ static void update(float* f, int*, float cm, const float* a, const float*, const float* b, int, int sel,
                                    const TileParams& P) {
 #pragma unroll
-        for (int k = 0; k < KS; ++k) f[0] += ex2_mixed<3>(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm), sel + k);
+        for (int k = 0; k < KS; ++k) f[0] += ex2_mixed<4>(fmaf(P.p, lg2_approx(fabsf(a[k] - b[k])), cm), sel + k);
     }
     __device__ static void combine(float* f, int*, const float* pf, const int*) { f[0] += pf[0]; }
     __device__ static float load_pres(const TileParams& P, int m, int n, int g) {
-        return -P.p * log2f(P.pres.ptr[out_offset(P.out, m, n, g)]);
+        return -P.p * log2f(pow_norm_of(P, m, n, g, out_offset(P.out, m, n, g)));
     }
     __device__ static void finalize(const float* f, const int*, float, int m, int n, int g, const TileParams& P) {
         const long long off = out_offset(P.out, m, n, g);
-        const float M = P.pres.ptr[off];
+        const float M = pow_norm_of(P, m, n, g, off);
+        if (P.guard != nullptr && !(f[0] >= kNormGuard)) *P.guard = 1;
         const float s = f[0] + exp2f(P.p * (log2f(kEps) - log2f(M)));
         P.out_f0[off] = M * powf(s, 1.0f / P.p);
     }

@@ -254,6 +254,36 @@ __global__ void rescan_kernel(Operand a0, Operand a1, Operand b, const float* __
         }
 }
 
+// out[g * rows + r] = max_k |v[g][r][k]|.  Contiguous k: one warp per row; k `stride_k` apart with neighbouring rows
+// contiguous (inputs read in place): one thread per row.  clear (may be null): a flag word the first thread resets.
+__global__ void row_absmax_kernel(Operand v, long long rows, int inner, int groups, float* __restrict__ out, int* clear) {
+    if (clear && blockIdx.x == 0 && threadIdx.x == 0) *clear = 0;
+    const int lane = threadIdx.x & 31;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    const long long total = rows * groups;
+    for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
+        const long long g = i / rows, r = i - g * rows;
+        const float* src = v.ptr + g * v.stride_group + r * v.stride_row;
+        float m = 0.0f;
+        for (int k = lane; k < inner; k += 32) m = fmaxf(m, fabsf(src[k]));
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        if (lane == 0) out[i] = m;
+    }
+}
+__global__ void row_absmax_strided_kernel(Operand v, long long rows, int inner, int groups, long long stride_k,
+                                          float* __restrict__ out, int* clear) {
+    if (clear && blockIdx.x == 0 && threadIdx.x == 0) *clear = 0;
+    const long long total = rows * groups;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long g = i / rows, r = i - g * rows;
+        const float* src = v.ptr + g * v.stride_group + r * v.stride_row;
+        float m = 0.0f;
+        for (int k = 0; k < inner; ++k) m = fmaxf(m, fabsf(src[k * stride_k]));
+        out[i] = m;
+    }
+}
+
 // gate (may be null): the kernel runs only if (*gate != 0) == run_if_nonzero
 __global__ void side_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, long long count, int tiles,
                                    bool accumulate, const int* gate, bool run_if_nonzero) {
@@ -394,6 +424,16 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
     if (mode == 0) rescan_kernel<0><<<grid, kBlock, 0, st>>>(a0, a1, b, y, pos, s, a_stride_k);
     else if (mode == 1) rescan_kernel<1><<<grid, kBlock, 0, st>>>(a0, a1, b, y, pos, s, a_stride_k);
     else rescan_kernel<2><<<grid, kBlock, 0, st>>>(a0, a1, b, y, pos, s, a_stride_k);
+    LDN_LAUNCH_RET();
+}
+
+int launch_row_absmax(Operand v, long long rows, int inner, int groups, long long stride_k, float* out, int* clear,
+                      cudaStream_t st) {
+    if (stride_k == 1)
+        row_absmax_kernel<<<blocks_for(rows * groups * 32), kBlock, 0, st>>>(v, rows, inner, groups, out, clear);
+    else
+        row_absmax_strided_kernel<<<blocks_for(rows * groups), kBlock, 0, st>>>(v, rows, inner, groups, stride_k, out,
+                                                                               clear);
     LDN_LAUNCH_RET();
 }
 

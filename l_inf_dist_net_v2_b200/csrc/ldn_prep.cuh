@@ -42,6 +42,11 @@ int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, co
 int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, int* pos, const Shape& s,
                   cudaStream_t st, long long a_stride_k);
 
+// out[g * rows + r] = max_k |v[g][r][k]| for an operand view with `inner` reduction elements per row, stride_k apart
+// (1: contiguous).  clear (may be null): a device word that the kernel resets to 0.
+int launch_row_absmax(Operand v, long long rows, int inner, int groups, long long stride_k, float* out, int* clear,
+                      cudaStream_t st);
+
 // grad_weight of the fused backward: gw[i] = -sum_t part[t * count + i], t < tiles
 // gate (may be null): the kernel runs only if (*gate != 0) == run_if_nonzero
 int launch_side_reduce(const float* part, float* gw, long long count, int tiles, bool accumulate, const int* gate,

@@ -751,3 +751,24 @@ def test_backward_in_channel_ranges_matches_whole(C, shape, p):
             assert rel_to_max(gx.cpu().numpy(), ogx) < rtol_for(p, True)
             assert rel_to_max(gw.cpu().numpy(), ogw) < rtol_for(p, True)
     C.check_status()
+
+
+@pytest.mark.parametrize("shape", [(70, 96, 40, 2, 1), (3, 40, 24, 2, 100), (130, 200, 150, 1, 1)])
+@pytest.mark.parametrize("p", [10.5, 37.5, 100.0])
+def test_general_p_forward_when_the_cheap_normaliser_is_too_loose(C, shape, p):
+    """For 10 < p <= 100 the forward normalises by max|x| + max|w| per output instead of the exact max |x - w|.  When
+    inputs and weights nearly coincide (differences of 1e-3 on values around 5) that bound is thousands of times
+    too large, every term underflows, and the library must notice and recompute with the exact maximum."""
+    B, CI, CO, G, HW = shape
+    rng = np.random.default_rng(23)
+    x = (5.0 + 1e-3 * rng.random((B, CI, HW))).astype(np.float32)
+    w = (5.0 + 1e-3 * rng.standard_normal((CO, CI // G))).astype(np.float32)
+    y = run_forward(C, x, w, p, G)
+    ref = oracle.norm_dist_forward(x, w, p, G)
+    assert np.isfinite(y.cpu().numpy()).all()
+    assert rel(y.cpu().numpy(), ref) < RTOL_GEN, (shape, p)
+    # and the ordinary case right behind it on the same stream (the guard word alternates between calls)
+    x2, w2, _ = make_inputs(shape, 24)
+    y2 = run_forward(C, x2, w2, p, G)
+    assert rel(y2.cpu().numpy(), oracle.norm_dist_forward(x2, w2, p, G)) < RTOL_GEN
+    C.check_status()
