@@ -309,13 +309,13 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
     if ((r = get_w_view(c, w, s, &wv)) != kOk) return r;
     float* side = nullptr;
     if (fused && !(side = c.bump.take<float>(side_floats))) return kWorkspace;
-    // the guard's flag: two words of the arena's status block used in turn, each call clears the next call's
+    // the guard's flag: a word of the arena's status block, cleared in stream order before the coefficient kernel
+    // may raise it (calls on one stream follow each other, so the previous call's gated kernels have read it by then)
     int* flag = nullptr;
-    int* flag_next = nullptr;
     if (guarded) {
-        const unsigned turn = c.arena->range_calls++ & 1u;
-        flag = c.arena->status + 1 + turn;
-        flag_next = c.arena->status + 1 + (turn ^ 1u);
+        flag = c.arena->status + 1;
+        const cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(int), c.st);
+        if (e != cudaSuccess) return cuda_status(e);
     }
 
     // the kernels of one arithmetic form (fam: 0..8 integer q, -1 / -2 general p) on coefficient views cv0 / cv1.
@@ -388,7 +388,7 @@ int norm_dist_backward_part(const float* go, const float* x, const float* w, con
         float* c0 = c.bump.take<float>(int_floats);
         if (!c0) return kWorkspace;
         const View cv = View{c0, s.COg, s.M, s.G, int_pitch, s.M * int_pitch, 1};
-        if ((r = launch_coef_int(go, y, c0, s, static_cast<int>(int_pitch), iq, flag, flag_next, c.st)) != kOk) return r;
+        if ((r = launch_coef_int(go, y, c0, s, static_cast<int>(int_pitch), iq, flag, c.st)) != kOk) return r;
         if ((r = run_family(iq, cv, cv, nullptr)) != kOk) return r;
         if (!guarded) return kOk;
         // second form, gated by the flag: 1 / y and g as coefficients, 2^(q lg2(|t| / y)) per pair
@@ -605,12 +605,11 @@ LDN_API int ldn_norm_dist_forward(const float* input, const float* weight, int B
         float* xa = c.bump.take<float>(static_cast<size_t>(xrows * xgroups));
         float* wa = c.bump.take<float>(static_cast<size_t>(s.CO));
         if (!xa || !wa) return kWorkspace;
-        // the guard word: two words of the arena's status block used in turn, each call clears the next call's
-        const unsigned turn = c.arena->norm_calls++ & 1u;
-        int* flag = c.arena->status + 3 + turn;
-        int* flag_next = c.arena->status + 3 + (turn ^ 1u);
+        // the guard word (a word of the arena's status block): cleared by the first row reduction, raised by the sum
+        // kernel, read by the gated kernels behind it -- all in stream order
+        int* flag = c.arena->status + 2;
         const Operand xop = inplace ? Operand{input, 1, static_cast<long long>(s.CIg) * s.HW} : as_operand(xv);
-        if ((r = launch_row_absmax(xop, xrows, s.CIg, static_cast<int>(xgroups), inplace ? s.HW : 1, xa, flag_next,
+        if ((r = launch_row_absmax(xop, xrows, s.CIg, static_cast<int>(xgroups), inplace ? s.HW : 1, xa, flag,
                                    c.st)) != kOk)
             return r;
         if ((r = launch_row_absmax(as_operand(wv), s.COg, s.CIg, s.G, 1, wa, nullptr, c.st)) != kOk) return r;
@@ -858,7 +857,7 @@ LDN_API int ldn_inf_dist_forward_nograd_noalloc(const float* input, const float*
     char* base = nullptr;
     if ((r = noalloc_scratch_address(&base)) != kOk) return r;
     Arena fixed{base + kNoAllocStatusBytes, kNoAllocScratchBytes - kNoAllocStatusBytes,
-                reinterpret_cast<int*>(base), nullptr, nullptr, 0u, 0u, false, nullptr};
+                reinterpret_cast<int*>(base), nullptr, nullptr, false, nullptr};
     c.arena = &fixed;
     c.bump = Bump{fixed.base, 0, fixed.capacity};
     View xv, wv;

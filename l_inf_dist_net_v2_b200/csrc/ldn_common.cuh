@@ -174,8 +174,6 @@ struct Arena {
     int* status_host;  // pinned host mirror used when checking
     void* call_mutex;  // std::mutex*: held for the length of one entry-point call, so that two host threads that
                        // use the same stream cannot interleave launches that share the scratch block
-    unsigned norm_calls;   // calls that used the guarded normaliser of the p > 10 forward (its two flag words alternate)
-    unsigned range_calls;  // calls that used the range guard of the integer-p backward (its two flag words alternate)
     bool graph_used;   // a call was issued on this arena while its stream was being captured
     void* retired;     // std::vector<void*>*: earlier blocks that captured graphs may still refer to
 };

@@ -56,7 +56,7 @@ int find_arena(cudaStream_t stream, Arena** out) {
         ent = new ArenaEntry();
         ent->device = dev;
         ent->stream = stream;
-        ent->arena = Arena{nullptr, 0, nullptr, nullptr, new std::mutex(), 0u, 0u, false, new std::vector<void*>()};
+        ent->arena = Arena{nullptr, 0, nullptr, nullptr, new std::mutex(), false, new std::vector<void*>()};
         auto drop = [&]() {
             delete static_cast<std::mutex*>(ent->arena.call_mutex);
             delete static_cast<std::vector<void*>*>(ent->arena.retired);

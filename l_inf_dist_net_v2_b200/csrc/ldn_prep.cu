@@ -103,15 +103,14 @@ __device__ __forceinline__ long long y_offset(const Shape& s, const CanonIdx& q)
 }
 
 // Range guard of the integer-q coefficient g / y^q: *flag is raised when some y^-q is outside [kRqMin, kRqMax]
-// (beyond: y^-q overflows or |t|^q <= y^q goes denormal; below: the coefficient loses its bits); the first thread
-// also clears the word the next call will use.  flag may be null (q = 0).
+// (beyond: y^-q overflows or |t|^q <= y^q goes denormal; below: the coefficient loses its bits).  The caller clears
+// the word beforehand; flag may be null (q = 0).
 constexpr float kRqMin = 1e-30f, kRqMax = 1e24f;
 __device__ __forceinline__ bool rq_unsafe(float rq) { return !(rq >= kRqMin && rq <= kRqMax); }
 
 __global__ void coef_int_kernel(const float* __restrict__ go, const float* __restrict__ y, float* __restrict__ coef,
-                                Shape s, int pitch, int iq, int* flag, int* flag_next) {
+                                Shape s, int pitch, int iq, int* flag) {
     const long long total = static_cast<long long>(s.G) * s.M * s.COg;
-    if (flag_next && blockIdx.x == 0 && threadIdx.x == 0) *flag_next = 0;
     bool bad = false;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const CanonIdx q = canon_idx(i, s.COg, s.M);
@@ -127,8 +126,7 @@ __global__ void coef_int_kernel(const float* __restrict__ go, const float* __res
 
 // flat fast paths (HW == 1, G == 1, pitch == COg: source and destination have the same element order)
 __global__ void coef_int_flat_kernel(const float4* __restrict__ go, const float4* __restrict__ y,
-                                     float4* __restrict__ coef, long long n4, int iq, int* flag, int* flag_next) {
-    if (flag_next && blockIdx.x == 0 && threadIdx.x == 0) *flag_next = 0;
+                                     float4* __restrict__ coef, long long n4, int iq, int* flag) {
     bool bad = false;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const float4 yv = y[i];
@@ -385,16 +383,15 @@ static bool flat_ok(const Shape& s, int pitch, const void* a, const void* b) {
 }
 
 int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, int* flag,
-                    int* flag_next, cudaStream_t st) {
+                    cudaStream_t st) {
     if (flat_ok(s, pitch, go, y)) {
         const long long n4 = static_cast<long long>(s.M) * s.COg / 4;
         coef_int_flat_kernel<<<blocks_for(n4), kBlock, 0, st>>>(reinterpret_cast<const float4*>(go),
                                                               reinterpret_cast<const float4*>(y),
-                                                              reinterpret_cast<float4*>(coef), n4, iq, flag, flag_next);
+                                                              reinterpret_cast<float4*>(coef), n4, iq, flag);
         LDN_LAUNCH_RET();
     }
-    coef_int_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, coef, s, pitch, iq, flag,
-                                                                                flag_next);
+    coef_int_kernel<<<blocks_for((long long)s.G * s.M * s.COg), kBlock, 0, st>>>(go, y, coef, s, pitch, iq, flag);
     LDN_LAUNCH_RET();
 }
 int launch_coef_gen(const float* go, const float* y, float* rinv, float* gcp, const Shape& s, int pitch,

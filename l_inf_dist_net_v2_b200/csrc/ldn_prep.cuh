@@ -21,9 +21,9 @@ int launch_canon_bounds(const float* xl, const float* xu, float* lc, float* uc, 
 // wc[g][o][pitch] <- w[(g COg + o) CIg + c]
 int launch_canon_w(const float* w, float* wc, const Shape& s, int pitch, cudaStream_t st);
 // integer p - 1 = iq:  coef[g][m][pitch] <- go / y^iq   (go, y in output layout).  flag (may be null): set to 1 when
-// some y^-iq is outside the range in which that coefficient times |t|^iq is accurate; flag_next (may be null): cleared.
+// some y^-iq is outside the range in which that coefficient times |t|^iq is accurate (cleared by the caller before).
 int launch_coef_int(const float* go, const float* y, float* coef, const Shape& s, int pitch, int iq, int* flag,
-                    int* flag_next, cudaStream_t st);
+                    cudaStream_t st);
 // general p: rinv[g][rows_pad][pitch] <- -q lg2 y (fold: the exponent offset of (|t| / y)^q) or 1 / y,
 // gcp[g][rows_pad][pitch] <- go; rows beyond M and columns beyond CO / G are padding (offset -1e30 resp. factor 0,
 // gradient factor 0)
