@@ -400,6 +400,7 @@ def run_ours(args, rank, world, local_rank, comm_group=None):
             model = model_block(args, rank, world, local_rank, comm_group)
         except Exception as exc:  # the headline line must survive a failure here
             model = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            lib.ldn_set_max_ctas(0)
         C.check_status()
 
     if rank != 0:
