@@ -20,8 +20,10 @@ int launch_fwd_variant_k(FwdKind kind, int reg_n, const TileLaunch& L, cudaStrea
         case FwdKind::PowInt: return by_width<FwdPowInt<8>>(reg_n, L, st);
         case FwdKind::PowGen: return by_width<FwdPowGen>(reg_n, L, st);
         case FwdKind::PowNorm: return by_width<FwdPowNorm>(reg_n, L, st);
-        case FwdKind::Inf: return by_width<FwdInf<false>>(reg_n, L, st);
-        case FwdKind::InfPos: return by_width<FwdInf<true>>(reg_n, L, st);
+        // (scalar subtractions: with a k-major A operand two neighbouring k of a row are not neighbouring registers;
+        // 64 x 576 x 1024 positions -> 128 outputs, value only: 0.58 -> 0.45 ms)
+        case FwdKind::Inf: return by_width<FwdInf<false, false>>(reg_n, L, st);
+        case FwdKind::InfPos: return by_width<FwdInf<true, false>>(reg_n, L, st);
         default: return kBadArgument;
     }
 }

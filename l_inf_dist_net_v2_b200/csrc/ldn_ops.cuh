@@ -196,6 +196,7 @@ struct FwdLayout {
     static constexpr bool SHORT_STAGES = false;  // stop a partly filled last stage after its valid k-groups
     static constexpr int UNROLL = 1;             // unroll factor of the rolled k-group loop (measured per op)
     static constexpr bool N_IN_SMEM = false;     // integer accumulators live in shared memory, not registers
+    static constexpr bool ROLLED_EPILOGUE = true;  // finalise a tile row by row in a rolled loop (small code)
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;        // output columns per thread: 8 (128 x 128 tile) or 4 (128 x 64)
     static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
@@ -353,9 +354,10 @@ __device__ __forceinline__ float col_epilogue(float v, int n, int g, const TileP
     return v;
 }
 
-template <bool POS>
+template <bool POS, bool PACK_K = true>
 struct FwdInf : FwdLayout {
     static constexpr bool N_IN_SMEM = POS;  // frees 64 registers of the indexed kernel (0.83 -> 0.79 ms)
+    static constexpr bool ROLLED_EPILOGUE = !POS;
     static constexpr bool SHORT_STAGES = !POS;
     static constexpr int UNROLL = 4;  // (128 x 64 tiles with two CTAs per SM: 0.556 ms against 0.548 ms)
     static constexpr int KSTEP = 4;  // few instructions per pair: wide shared-memory reads, fewer loop trips
@@ -379,11 +381,18 @@ struct FwdInf : FwdLayout {
         // The subtraction is packed along k (both operands arrive as neighbouring registers of a 16-byte shared-memory
         // read): one issue slot for two differences.  Every kernel of this family is bound by the issue rate
         // (one warp instruction per scheduler and clock), not by a pipe; measured 0.572 -> 0.548 ms.
+        // (PACK_K = false: a k-major A operand delivers one k of four rows per read, so two neighbouring k of a row
+        // are not neighbouring registers and every packed operand would first be moved together)
         static_assert(KS % 2 == 0, "packed subtraction walks k in pairs");
+        if constexpr (PACK_K) {
 #pragma unroll
-        for (int k = 0; k < KS; k += 2) {
-            const float2 d = pk_sub(make_float2(a[k], a[k + 1]), make_float2(b[k], b[k + 1]));
-            m = fmaxf(fmaxf(m, fabsf(d.x)), fabsf(d.y));
+            for (int k = 0; k < KS; k += 2) {
+                const float2 d = pk_sub(make_float2(a[k], a[k + 1]), make_float2(b[k], b[k + 1]));
+                m = fmaxf(fmaxf(m, fabsf(d.x)), fabsf(d.y));
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < KS; ++k) m = fmaxf(m, fabsf(a[k] - b[k]));
         }
     }
     // end of a 32-channel stage: stages are visited in ascending order, so a strict comparison keeps the
@@ -461,6 +470,7 @@ struct FwdBound : FwdLayout {
 template <bool UPPER>
 struct FwdBoundPos : FwdLayout {
     static constexpr bool N_IN_SMEM = true;
+    static constexpr bool ROLLED_EPILOGUE = false;
     static constexpr int STAGES = 3;  // 3 x 48 KB of operand tiles + 64 KB of stage ids
     static constexpr int KSTEP = 4;
     static constexpr int UNROLL = 2;
@@ -519,6 +529,7 @@ struct FwdBoundPos : FwdLayout {
 // kernels above.
 struct FwdBoundBoth : FwdLayout {
     static constexpr bool N_IN_SMEM = true;
+    static constexpr bool ROLLED_EPILOGUE = false;
     static constexpr int REG_N = 4;
     static constexpr int KSTEP = 4;
     static constexpr int UNROLL = 1;
@@ -602,6 +613,7 @@ struct BwdLayout {
     static constexpr bool SHORT_STAGES = false;
     static constexpr int UNROLL = 1;
     static constexpr bool N_IN_SMEM = false;
+    static constexpr bool ROLLED_EPILOGUE = false;
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;
     static constexpr int CTAS_PER_SM = 1;

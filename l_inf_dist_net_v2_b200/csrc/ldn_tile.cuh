@@ -258,7 +258,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < RN; ++j) {
                     Op::init(accf[i][j], iacc(i, j));
-                    if (Op::HAS_P) {
+                    if (Op::HAS_P && !Op::ROLLED_EPILOGUE) {
                         const int m = tc.m0 + own_index<Op::LA>(tm, i);
                         const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
                         pres[i][j] = (m < P.M && n < P.N) ? Op::load_pres(P, m, n, tc.g) : 0.0f;
@@ -266,6 +266,23 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                         pres[i][j] = 0.0f;
                     }
                 }
+            if constexpr (Op::HAS_P && Op::ROLLED_EPILOGUE) {
+                // one register row per trip of a rolled loop (see the epilogue below): the rows move down one
+                // slot per trip, the row loaded in trip i ends in slot i
+#pragma unroll 1
+                for (int i = 0; i < kRegM; ++i) {
+#pragma unroll
+                    for (int r = 0; r + 1 < kRegM; ++r)
+#pragma unroll
+                        for (int j = 0; j < RN; ++j) pres[r][j] = pres[r + 1][j];
+                    const int m = tc.m0 + own_index<Op::LA>(tm, i);
+#pragma unroll
+                    for (int j = 0; j < RN; ++j) {
+                        const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
+                        pres[kRegM - 1][j] = (m < P.M && n < P.N) ? Op::load_pres(P, m, n, tc.g) : 0.0f;
+                    }
+                }
+            }
         }
 
         // A wait that runs out: the thread records the status and returns; the host reads the status word
@@ -430,15 +447,47 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 
         if (kt == KT - 1 || it == it1 - 1) {
             const bool whole = (seg_begin == tile * KT) && (kt == KT - 1);
-            if (whole) {
-#pragma unroll
-                for (int i = 0; i < kRegM; ++i)
+            if (whole && Op::ROLLED_EPILOGUE) {
+                // Ops with ROLLED_EPILOGUE finalise one register row per trip of a rolled loop: each trip handles row 0
+                // and moves the other rows down one slot (registers cannot be indexed by the trip count).  As
+                // straight-line code for all 64 outputs the epilogue is tens of KB of instructions that run once per
+                // tile and are fetched from memory every time: for the forward kernels 4 - 5 % of a 96-stage tile and
+                // 12 - 16 % of an 18-stage one.  (The backward and the index-tracking kernels were no faster with it.)
+#pragma unroll 1
+                for (int i = 0; i < RM; ++i) {
+                    const int m = tc.m0 + own_index<Op::LA>(tm, i);
 #pragma unroll
                     for (int j = 0; j < RN; ++j) {
-                        const int m = tc.m0 + own_index<Op::LA>(tm, i);
                         const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
-                        if (m < P.M && n < P.N) Op::finalize(accf[i][j], iacc(i, j), pres[i][j], m, n, tc.g, P);
+                        int* ia;
+                        if constexpr (Op::N_IN_SMEM) ia = ints + (i * RN + j) * kThreads + tid;
+                        else ia = acci[0][j];
+                        if (m < P.M && n < P.N) Op::finalize(accf[0][j], ia, pres[0][j], m, n, tc.g, P);
                     }
+#pragma unroll
+                    for (int r = 0; r + 1 < RM; ++r)
+#pragma unroll
+                        for (int j = 0; j < RN; ++j) {
+#pragma unroll
+                            for (int a = 0; a < NF; ++a) accf[r][j][a] = accf[r + 1][j][a];
+                            if (Op::HAS_P) pres[r][j] = pres[r + 1][j];
+                            if constexpr (!Op::N_IN_SMEM) {
+#pragma unroll
+                                for (int a = 0; a < NI; ++a) acci[r][j][a] = acci[r + 1][j][a];
+                            }
+                        }
+                }
+            } else if (whole) {
+                if constexpr (!Op::ROLLED_EPILOGUE) {
+#pragma unroll
+                    for (int i = 0; i < kRegM; ++i)
+#pragma unroll
+                        for (int j = 0; j < RN; ++j) {
+                            const int m = tc.m0 + own_index<Op::LA>(tm, i);
+                            const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
+                            if (m < P.M && n < P.N) Op::finalize(accf[i][j], iacc(i, j), pres[i][j], m, n, tc.g, P);
+                        }
+                }
             } else {
                 const int slot = (tile == first_tile) ? 0 : 1;
                 float* dst = P.partials +
