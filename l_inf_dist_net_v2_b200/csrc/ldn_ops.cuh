@@ -197,6 +197,7 @@ struct FwdLayout {
     static constexpr int UNROLL = 1;             // unroll factor of the rolled k-group loop (measured per op)
     static constexpr bool N_IN_SMEM = false;     // integer accumulators live in shared memory, not registers
     static constexpr bool ROLLED_EPILOGUE = true;  // finalise a tile row by row in a rolled loop (small code)
+    static constexpr bool ROLLED_PRES = true;      // the same for loading the resident per-output operand
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;        // output columns per thread: 8 (128 x 128 tile) or 4 (128 x 64)
     static constexpr int CTAS_PER_SM = 1;  // 2 needs REG_N = 4 (registers) and at most 113 KB of shared memory
@@ -613,7 +614,8 @@ struct BwdLayout {
     static constexpr bool SHORT_STAGES = false;
     static constexpr int UNROLL = 1;
     static constexpr bool N_IN_SMEM = false;
-    static constexpr bool ROLLED_EPILOGUE = false;
+    static constexpr bool ROLLED_EPILOGUE = false;  // measured: no gain for the backward kernels (160-stage tiles)
+    static constexpr bool ROLLED_PRES = false;
     static constexpr int STAGES = kStages;
     static constexpr int REG_N = 8;
     static constexpr int CTAS_PER_SM = 1;

@@ -258,7 +258,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < RN; ++j) {
                     Op::init(accf[i][j], iacc(i, j));
-                    if (Op::HAS_P && !Op::ROLLED_EPILOGUE) {
+                    if (Op::HAS_P && !Op::ROLLED_PRES) {
                         const int m = tc.m0 + own_index<Op::LA>(tm, i);
                         const int n = tc.n0 + own_index<Op::LB, RN>(tn, j);
                         pres[i][j] = (m < P.M && n < P.N) ? Op::load_pres(P, m, n, tc.g) : 0.0f;
@@ -266,7 +266,7 @@ tile_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ 
                         pres[i][j] = 0.0f;
                     }
                 }
-            if constexpr (Op::HAS_P && Op::ROLLED_EPILOGUE) {
+            if constexpr (Op::HAS_P && Op::ROLLED_PRES) {
                 // one register row per trip of a rolled loop (see the epilogue below): the rows move down one
                 // slot per trip, the row loaded in trip i ends in slot i
 #pragma unroll 1
