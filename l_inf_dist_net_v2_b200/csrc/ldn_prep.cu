@@ -4,6 +4,7 @@ namespace ldn {
 
 namespace {
 constexpr int kBlock = 256;
+constexpr int kRescanInplaceMaxSmem = 200 * 1024;  // input slab of rescan_inplace_kernel
 constexpr int kRescanChunk = 1024;  // outputs a block of rescan_kernel handles in one pass (a multiple of kBlock / 8)
 // grid of a kernel that usually returns at once (gated): small, the grid-stride loops cover the rest when it runs
 inline unsigned gated_blocks(unsigned blocks, const int* gate) { return (gate && blocks > 592u) ? 592u : blocks; }
@@ -252,6 +253,88 @@ __global__ void rescan_kernel(Operand a0, Operand a1, Operand b, const float* __
         }
 }
 
+// The same search for inputs read in place (x[B, C, HW]: the channels of an output are HW floats apart, so the
+// kernel above pulls one 32-byte sector per channel and output from L2).  Here a block owns P neighbouring
+// positions of one (sample, group): it copies their CI/G x P input values to shared memory once (rows of P floats,
+// coalesced), then every thread scans the 32 channels of its output's stage there; a warp holds P consecutive
+// positions of 32 / P outputs, so y / pos are read and written coalesced and the shared-memory reads are
+// conflict-free whatever the lanes' stages.  The weight pieces (one 128-byte run per output and stage) come from L1 / L2.
+template <int P>
+__global__ void __launch_bounds__(kBlock) rescan_inplace_kernel(Operand a0, Operand b, const float* __restrict__ y,
+                                                                int* __restrict__ pos, Shape s) {
+    extern __shared__ float4 xs4[];
+    float* xs = reinterpret_cast<float*>(xs4);  // [CI/G][P]
+    constexpr int V = P / 4;
+    const long long bg = blockIdx.x;
+    const int g = static_cast<int>(bg % s.G);
+    const int hw0 = blockIdx.y * P;
+    const float* xsrc = a0.ptr + bg * a0.stride_group;
+    for (int idx = threadIdx.x; idx < s.CIg * V; idx += kBlock) {
+        const int c = idx / V, v = idx - c * V;
+        const int hw = hw0 + 4 * v;
+        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (hw < s.HW) val = *reinterpret_cast<const float4*>(xsrc + static_cast<long long>(c) * s.HW + hw);
+        xs4[idx] = val;
+    }
+    __syncthreads();
+    const int hl = threadIdx.x % P;
+    const int hw = hw0 + hl;
+    if (hw >= s.HW) return;
+    const int kpad = (s.CIg + 3) & ~3;
+    const float* brow = b.ptr + g * b.stride_group;
+    const long long base = bg * (static_cast<long long>(s.COg) * s.HW) + hw;
+    for (int o = threadIdx.x / P; o < s.COg; o += kBlock / P) {
+        const long long i = base + static_cast<long long>(o) * s.HW;
+        const int stage = pos[i];
+        int result = 0;
+        if (stage >= 0) {
+            const float yv = y[i];
+            const int k0 = stage * 32;
+            const float* wr = brow + o * b.stride_row + k0;
+            int best = -1;
+            bool neg = false;
+#pragma unroll
+            for (int c4 = 7; c4 >= 0; --c4) {
+                const int k = k0 + 4 * c4;
+                if (k < kpad) {
+                    const float4 wv = *reinterpret_cast<const float4*>(wr + 4 * c4);
+                    const float we[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                    for (int e = 3; e >= 0; --e) {
+                        if (k + e < s.CIg) {
+                            const float d = xs[(k + e) * P + hl] - we[e];
+                            if (fabsf(d) == yv) {
+                                best = k + e;
+                                neg = d < 0.0f;
+                            }
+                        }
+                    }
+                }
+            }
+            if (best >= 0) result = best | (neg ? static_cast<int>(0x80000000u) : 0);
+        }
+        pos[i] = result;
+    }
+}
+
+template <int P>
+int launch_rescan_inplace(Operand a0, Operand b, const float* y, int* pos, const Shape& s, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem = s.CIg * P * static_cast<int>(sizeof(float));
+    if (dev >= 64 || !configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(rescan_inplace_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kRescanInplaceMaxSmem);
+        if (e != cudaSuccess) return cuda_status(e);
+        if (dev < 64) configured[dev] = true;
+    }
+    const dim3 grid(static_cast<unsigned>(static_cast<long long>(s.B) * s.G), static_cast<unsigned>((s.HW + P - 1) / P));
+    rescan_inplace_kernel<P><<<grid, kBlock, smem, st>>>(a0, b, y, pos, s);
+    count_launches(1);
+    return cuda_status(cudaGetLastError());
+}
+
 // out[g * rows + r] = max_k |v[g][r][k]|.  Contiguous k: one warp per row; k `stride_k` apart with neighbouring rows
 // contiguous (inputs read in place): one thread per row.  clear (may be null): a flag word the first thread resets.
 __global__ void row_absmax_kernel(Operand v, long long rows, int inner, int groups, float* __restrict__ out, int* clear) {
@@ -415,6 +498,18 @@ int launch_rescan(int mode, Operand a0, Operand a1, Operand b, const float* y, i
     const long long cohw = static_cast<long long>(s.COg) * s.HW;
     const long long bg = static_cast<long long>(s.B) * s.G;
     if (cohw > 0x7fffffffLL || bg > 0x7fffffffLL) return kBadArgument;
+    if (mode == 0 && a_stride_k != 1 && a_stride_k == s.HW && a0.stride_row == 1 && (s.HW & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(a0.ptr) & 15u) == 0 && (s.HW + 7) / 8 <= 65535) {
+        // inputs read in place: the largest slab of positions that leaves room for two blocks per SM, else the
+        // largest that fits at all; beyond that (CI/G > 6400) the general kernel
+        const long long row = static_cast<long long>(s.CIg) * sizeof(float);
+        for (int pass = 0; pass < 2; ++pass) {
+            const long long limit = pass == 0 ? 96 * 1024 : kRescanInplaceMaxSmem;
+            if (row * 32 <= limit) return launch_rescan_inplace<32>(a0, b, y, pos, s, st);
+            if (row * 16 <= limit) return launch_rescan_inplace<16>(a0, b, y, pos, s, st);
+            if (row * 8 <= limit) return launch_rescan_inplace<8>(a0, b, y, pos, s, st);
+        }
+    }
     long long chunks = (cohw + kRescanChunk - 1) / kRescanChunk;
     if (chunks > 65535) chunks = 65535;  // the kernel strides over the rest
     const dim3 grid(static_cast<unsigned>(bg), static_cast<unsigned>(chunks));

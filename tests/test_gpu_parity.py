@@ -282,6 +282,29 @@ def test_fused_backward_in_row_chunks(C, shape, p):
     C.check_status()
 
 
+@pytest.mark.parametrize("ci,hw", [(1000, 96), (2000, 100), (3100, 96), (5000, 100), (6500, 96)])
+def test_index_search_of_inputs_read_in_place(C, ci, hw):
+    """x[B, C, HW] read in place: the index search keeps a slab of 32, 16 or 8 positions x all channels in shared
+    memory (chosen by the reduction length; beyond 6400 channels the general search runs).  Equal maxima inside a
+    stage and across stages must give the first channel (inf_dist_cuda.cu:173-177)."""
+    rng = np.random.default_rng(ci)
+    B, CO = 2, 12
+    x = rng.random((B, ci, hw), dtype=np.float32)
+    w = rng.standard_normal((CO, ci)).astype(np.float32)
+    # channels 7 and 45 repeat channel 3 (same stage / next stage); make that channel the maximum for some outputs
+    for k in (7, 45):
+        x[:, k] = x[:, 3]
+        w[:, k] = w[:, 3]
+    w[::3, 3] = w[::3, 7] = w[::3, 45] = 9.0
+    oy, opos = oracle.inf_dist_forward(x, w, 1)
+    y = torch.empty(B, CO, hw, device="cuda")
+    pos = torch.empty(B, CO, hw, device="cuda", dtype=torch.int32)
+    C.inf_dist_forward(dev(x), dev(w), y, pos, 1)
+    assert np.array_equal(y.cpu().numpy(), oy)
+    assert np.array_equal(pos.cpu().numpy(), opos)
+    assert (opos[:, ::3] & 0x7fffffff == 3).all()
+
+
 @pytest.mark.parametrize("shape", SHAPES)
 def test_inf_family_against_checker(C, shape):
     from l_inf_dist_net_v2_b200._lib import lib
