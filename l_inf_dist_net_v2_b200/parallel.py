@@ -113,8 +113,9 @@ class OverlappedDataParallel:
         as with the full update on every rank, but the memory-bound optimiser pass (28 bytes per parameter for Adam)
         shrinks by the world size.  The whole chain (reduce-scatter, slice update, all-gather, layer after layer in
         forward order) is issued on a side stream by `step()`; a layer's forward pre-hook only waits for that layer's
-        all-gather.  Off by default: the slice updates then run on the few SMs the distance kernels leave free, and on
-        two GPUs the step of the hybrid model took 12.5 ms with it against 7.5 ms without.
+        all-gather.  Off by default: the slice updates then run on the few SMs the distance kernels leave free and the
+        two collectives of a layer take longer than its one all-reduce; the step of the hybrid model at p = inf took
+        12.5 ms with it against 7.5 ms without on two GPUs, 13.0 against 13.4 ms on four, 8.4 against 7.6 ms on eight.
 
     `optimizer_factory(params)` builds one optimiser per layer (any torch.optim optimiser, or optim.FusedAdam /
     FusedSGD); with shard_updates its parameters are 1-D slices that alias the layer's parameters.  Call `finish()`
